@@ -1,0 +1,150 @@
+/*
+ * b200attn -- C ABI of the B200 (sm_100a) GPT-OSS attention forward/backward library.
+ *
+ * The reference project has no native interface: its device code is three Triton kernels
+ * launched from Python (attention_kernel.py:244-262, :305-313, :316-339).  Each entry point
+ * below stands in for one of those launch sites (or for the host code around it) and is
+ * what a host-language binding for this path would bind.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless said otherwise.  The library allocates no
+ *     device memory and keeps none after a call returns; all buffers belong to the caller
+ *     (as in the reference, where they are torch tensors: attention_kernel.py:241-242,
+ *     :295-298).
+ *   - Calls only enqueue work on `stream` of `device`; they never synchronise.
+ *   - Return value: 0 on success, a negative B200ATTN_E* code otherwise.  Nothing throws,
+ *     exits or traps.  `status`, when not NULL, is a device int32 the kernels OR a non-zero
+ *     code into if a bounded device-side wait gave up (it is never written on success); the
+ *     caller zeroes it and reads it back after synchronising.
+ *   - Tensors are bf16 4-D views (batch, head, position, head_dim) described by element
+ *     strides; the head_dim stride must be 1, pointers 16-byte aligned and the other strides
+ *     multiples of 8 elements -- the constraints the reference inherits from its TMA tensor
+ *     descriptors (attention_kernel.py:245-251).  Any permutation of the outer three
+ *     dimensions is therefore accepted: (B,H,S,d) as the attention module passes q/k/v, or
+ *     (B,S,H,d) as it expects the output (attention_kernel.py:272).
+ *   - Masking: key j is visible to query i of sequence b iff j <= i, j > i - window (when
+ *     window > 0) and j < seqlens[b]; rows i >= seqlens[b] are padding (o = 0, no gradient).
+ *     The reference ignores padding (attention_kernel.py:348-358); seqlens == NULL gives
+ *     exactly its behaviour.
+ */
+#ifndef B200ATTN_H_
+#define B200ATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200ATTN_VERSION 1
+#define B200ATTN_ROW_TILE 128 /* lse/delta rows are padded to a multiple of this */
+
+enum {
+  B200ATTN_OK = 0,
+  B200ATTN_EINVAL = -1,      /* NULL params / pointer, non-positive size          */
+  B200ATTN_ESHAPE = -2,      /* Hq % Hkv != 0, window < 0, S too large            */
+  B200ATTN_EHEADDIM = -3,    /* head_dim other than 64                            */
+  B200ATTN_EALIGN = -4,      /* pointer not 16-byte aligned / stride not % 8      */
+  B200ATTN_EDEVICE = -5,     /* device is not compute capability 10.x             */
+  B200ATTN_ECUDA = -6,       /* a CUDA runtime/driver call failed                 */
+  B200ATTN_ETENSORMAP = -7,  /* the driver rejected a TMA tensor map              */
+  B200ATTN_ESCRATCH = -8     /* scratch buffer missing or too small               */
+};
+
+/* bf16 tensor view (batch, head, position, head_dim); strides in ELEMENTS, head_dim stride 1 */
+typedef struct b200attn_tensor {
+  void* ptr;
+  int64_t stride_b;
+  int64_t stride_h;
+  int64_t stride_s;
+} b200attn_tensor;
+
+typedef struct b200attn_params {
+  /* problem size: q/o/dO/dq have Hq heads, k/v/dk/dv have Hkv heads, all have S positions */
+  int32_t B, Hq, Hkv, S, d;
+  int32_t window;          /* 0 = full causal, W > 0 = causal sliding window of W keys (incl. self) */
+  float scale;             /* logits multiplier, 1/sqrt(d) for GPT-OSS */
+  int32_t device;          /* CUDA device ordinal the pointers live on */
+  void* stream;            /* cudaStream_t (0 = legacy default stream) */
+  int32_t* status;         /* device int32, may be NULL */
+  const int32_t* seqlens;  /* (B) valid lengths for right-padded batches, may be NULL */
+  const float* sinks;      /* (Hq) fp32 per-head sink logits */
+
+  b200attn_tensor q, k, v; /* inputs */
+  b200attn_tensor o;       /* forward output; backward input */
+  float* lse;              /* (B,Hq,S_pad) fp32, S_pad = b200attn_padded_len(S): natural-log
+                              softmax denominator incl. the sink; forward output, backward input */
+
+  /* backward only */
+  b200attn_tensor d_o;        /* gradient of o */
+  b200attn_tensor dq, dk, dv; /* outputs, fully overwritten (no pre-zeroing needed) */
+  float* delta;               /* (B,Hq,S_pad) fp32 scratch: rowsum(dO*O) */
+  float* dsinks;              /* (Hq) fp32 output, overwritten */
+  float* dsinks_partial;      /* fp32 scratch of b200attn_dsinks_scratch_floats() elements */
+} b200attn_params;
+
+/* Library/ABI version (B200ATTN_VERSION the library was built with). */
+int b200attn_version(void);
+
+/* sizeof(b200attn_params) as the library was compiled, so that a binding written in another
+ * language can verify its own mirror of the struct before the first call. */
+size_t b200attn_sizeof_params(void);
+
+/* Static description of a return code.  Never NULL. */
+const char* b200attn_strerror(int code);
+
+/* S rounded up to the row tile: the S_pad of lse/delta. */
+int64_t b200attn_padded_len(int64_t S);
+
+/* Number of floats `dsinks_partial` must hold for this problem. */
+int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p);
+
+/*
+ * Forward: o = softmax_with_sink(q k^T * scale + mask) v, lse.
+ * Replaces the `_attn_fwd[grid](...)` launch and the pad / transpose copies around it
+ * (attention_kernel.py:230-262, :272).  Reads q,k,v,sinks,seqlens; writes o, lse.
+ */
+int b200attn_fwd(const b200attn_params* p);
+
+/*
+ * Backward: dq, dk, dv, dsinks from q,k,v,o,lse,dO.  Enqueues, in order, the four stages
+ * below.  Replaces attention_kernel.py:290-339 (dO transpose copy, zero-fills, the
+ * `_attn_bwd_precompute_D` launch and the `_attn_bwd` launch).
+ */
+int b200attn_bwd(const b200attn_params* p);
+
+/* Backward stages, exported separately so that each can be timed and tested alone. */
+
+/* delta = rowsum(dO * O) and per-block partial sums of -exp(sink - lse) * delta.
+ * Replaces `_attn_bwd_precompute_D` (attention_kernel.py:102-120) and the dSinks part of
+ * `_attn_bwd` (:173-176).  Writes delta, dsinks_partial. */
+int b200attn_bwd_preprocess(const b200attn_params* p);
+
+/* dsinks[h] = sum of the partials (fixed order, warp-shuffle tree: deterministic, unlike the
+ * reference's atomics at attention_kernel.py:176).  Reads dsinks_partial; writes dsinks. */
+int b200attn_bwd_dsinks(const b200attn_params* p);
+
+/* dk, dv: one CTA owns a 128-key tile of one KV head and loops over the query heads of the
+ * group and the query tiles that see it; no atomics (the reference accumulates through
+ * global atomics, attention_kernel.py:201-212).  Reads q,k,v,dO,lse,delta. */
+int b200attn_bwd_dkdv(const b200attn_params* p);
+
+/* dq: one CTA owns a 128-row query tile of one head (attention_kernel.py:214-217). */
+int b200attn_bwd_dq(const b200attn_params* p);
+
+/*
+ * Self-test of the tensor-core building blocks, used by the test-suite: D = A * B^T for one
+ * 128 x N x K tile through TMA + tcgen05.  No counterpart in the reference.
+ *   mode 0: A (128 x K) and B (N x K) both K-contiguous in shared memory, K = 64, N = 128
+ *   mode 1: A from tensor memory (bf16), B given as (K x N) row-major, i.e. N-contiguous,
+ *           K = 128, N = 64
+ * a, b: bf16 row-major matrices as described; d: fp32 (128 x N) row-major.
+ */
+int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int32_t* status, int device,
+                           void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200ATTN_H_ */

@@ -1,0 +1,11 @@
+"""B200-native GPT-OSS attention forward/backward (sinks, GQA, causal / sliding window).
+
+Public surface, matching the reference project's two modules:
+
+* ``attention_kernel``: ``attention``, ``triton_flash_attention`` / ``b200_flash_attention``
+* ``patching``: ``patch_flash_attention``, ``unpatch_flash_attention`` (imports transformers)
+"""
+from .attention_kernel import attention, b200_flash_attention, triton_flash_attention  # noqa: F401
+
+__all__ = ["attention", "b200_flash_attention", "triton_flash_attention"]
+__version__ = "0.1.0"

@@ -1,0 +1,90 @@
+// Shared definitions of the attention kernels: tile constants, kernel argument block,
+// visibility rule, and the UMMA descriptors of the three operand forms they use.
+#pragma once
+#include <cuda.h>
+
+#include "sm100_ptx.cuh"
+
+namespace b200attn {
+
+constexpr int kTile = 128;                     // query rows / keys per tile
+constexpr int kHeadDim = 64;                   // head_dim (one 128-byte swizzle row of bf16)
+constexpr int kTileBytes = kTile * kHeadDim * 2;  // 16 KB: one (128 x 64) bf16 tile
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+constexpr int kComputeThreads = 128;           // warps 0-3: one thread per tile row / TMEM lane
+constexpr int kThreads = kComputeThreads + 32; // warp 4: TMA producer + MMA issuer (lane 0)
+
+constexpr int kStatusWaitTimeout = 1;          // OR-ed into *status when a bounded wait gave up
+
+struct StridedPtr {  // bf16 (B,H,S,d) view, element strides, d stride 1
+  __nv_bfloat16* ptr;
+  long long sb, sh, ss;
+  __device__ __forceinline__ __nv_bfloat16* row(int b, int h, int s) const {
+    return ptr + b * sb + h * sh + (long long)s * ss;
+  }
+};
+
+struct KernelArgs {
+  int B, Hq, Hkv, S, S_pad, group;  // group = Hq / Hkv
+  int window;                       // 0 = full causal
+  float scale;                      // logits multiplier
+  float scale_log2;                 // scale * log2(e)
+  const int* seqlens;               // (B) or nullptr
+  const float* sinks;               // (Hq)
+  int* status;                      // may be nullptr
+  float* lse;                       // (B,Hq,S_pad), natural log
+  float* delta;                     // (B,Hq,S_pad)
+  float* dsinks;                    // (Hq)
+  float* dsinks_partial;            // (Hq, B * S_pad/128)
+  StridedPtr o, d_o, dq, dk, dv;    // tensors touched with plain loads/stores
+};
+
+__device__ __forceinline__ int seq_len(const KernelArgs& a, int b) {
+  if (a.seqlens == nullptr) return a.S;
+  int L = a.seqlens[b];
+  return L < 0 ? 0 : (L > a.S ? a.S : L);
+}
+
+// key j visible to query i (both already known to be < len where that matters)
+__device__ __forceinline__ bool visible(int i, int j, int window, int len) {
+  return (j <= i) && (window == 0 || j > i - window) && (i < len);
+}
+
+// Does a (query tile at q0, key tile at kv0) pair contain any masked (i, j)?
+__device__ __forceinline__ bool tile_needs_mask(int q0, int kv0, int window, int len) {
+  return (kv0 + kTile - 1 > q0) || (window != 0 && kv0 <= q0 + kTile - 1 - window) || (q0 + kTile > len);
+}
+
+// ---- UMMA operand descriptors --------------------------------------------------------
+// All shared-memory operand tiles are (128 rows x 64 bf16) written by TMA with the 128-byte
+// swizzle.  Read with rows as M/N and columns as K ("K-major"), one MMA K-step of 16 is 32
+// bytes along the row.  Read with rows as K and columns as M/N ("MN-major", 64 = exactly one
+// swizzle atom wide), one K-step of 16 is 16 rows = 2048 bytes.
+__device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
+  return make_smem_desc_sw128(smem_addr, 16, 1024);
+}
+__device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr) {
+  return make_smem_desc_sw128(smem_addr, kTileBytes, 1024);
+}
+constexpr uint32_t kDescKStepKMajor = 32 >> 4;     // +32 B per K-step, in 16-byte units
+constexpr uint32_t kDescKStepMNMajor = 2048 >> 4;  // +2048 B per K-step
+
+// Record a timed-out wait for the host.
+__device__ __forceinline__ void report_abort(const KernelArgs& a) {
+  if (a.status != nullptr) atomicOr(a.status, kStatusWaitTimeout);
+}
+
+// 16-byte vector store of 8 bf16 values given as 4 packed words
+__device__ __forceinline__ void store_bf16x8(__nv_bfloat16* dst, uint32_t w0, uint32_t w1, uint32_t w2,
+                                             uint32_t w3) {
+  *reinterpret_cast<uint4*>(dst) = make_uint4(w0, w1, w2, w3);
+}
+
+__device__ __forceinline__ void zero_row(__nv_bfloat16* dst) {
+#pragma unroll
+  for (int c = 0; c < kHeadDim; c += 8) store_bf16x8(dst + c, 0u, 0u, 0u, 0u);
+}
+
+}  // namespace b200attn

@@ -1,0 +1,280 @@
+// C ABI of the library (declared in include/b200attn.h): argument validation, TMA tensor
+// maps, kernel launches.  No device memory is allocated here and nothing synchronises.
+#include "../../include/b200attn.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "attn_common.cuh"
+#include "bwd_dkdv_kernel.cuh"
+#include "bwd_dq_kernel.cuh"
+#include "bwd_preprocess_kernel.cuh"
+#include "fwd_kernel.cuh"
+#include "umma_selftest.cuh"
+
+namespace {
+
+using namespace b200attn;
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver entry point is looked up once; the pointer is immutable afterwards.
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+        q != cudaDriverEntryPointSuccess)
+      return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// Makes `device` current for the duration of a call and restores the caller's device after.
+struct DeviceGuard {
+  int prev = -1;
+  bool ok = true;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
+    if (prev != device && cudaSetDevice(device) != cudaSuccess) ok = false;
+  }
+  ~DeviceGuard() {
+    int cur = -1;
+    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
+  }
+};
+
+int check_device(int device) {
+  int major = 0;
+  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) return B200ATTN_ECUDA;
+  return major == 10 ? B200ATTN_OK : B200ATTN_EDEVICE;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// A dimension of extent 1 may carry any stride; give it a harmless one.
+int64_t usable_stride(int64_t stride, int64_t extent, int64_t fallback) { return extent == 1 ? fallback : stride; }
+
+int check_tensor(const b200attn_tensor& t, int B, int H, int S) {
+  if (t.ptr == nullptr) return B200ATTN_EINVAL;
+  if (!aligned16(t.ptr)) return B200ATTN_EALIGN;
+  const int64_t ss = usable_stride(t.stride_s, S, kHeadDim), sh = usable_stride(t.stride_h, H, kHeadDim),
+                sb = usable_stride(t.stride_b, B, kHeadDim);
+  if (ss % 8 || sh % 8 || sb % 8 || ss < kHeadDim || sh <= 0 || sb <= 0) return B200ATTN_EALIGN;
+  return B200ATTN_OK;
+}
+
+// 4-D bf16 map (d, S, H, B) with a (64 x rows) box and the 128-byte swizzle.
+int make_map(CUtensorMap* map, const b200attn_tensor& t, int B, int H, int S, int box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return B200ATTN_ECUDA;
+  const int64_t ss = usable_stride(t.stride_s, S, kHeadDim), sh = usable_stride(t.stride_h, H, (int64_t)S * ss),
+                sb = usable_stride(t.stride_b, B, (int64_t)S * ss);
+  cuuint64_t dims[4] = {(cuuint64_t)kHeadDim, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {(cuuint32_t)kHeadDim, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ETENSORMAP;
+}
+
+StridedPtr strided(const b200attn_tensor& t) {
+  return StridedPtr{static_cast<__nv_bfloat16*>(t.ptr), (long long)t.stride_b, (long long)t.stride_h, (long long)t.stride_s};
+}
+
+enum Need { kNeedFwd = 1, kNeedBwdIn = 2, kNeedDelta = 4, kNeedPartial = 8, kNeedDq = 16, kNeedDkv = 32, kNeedDsinks = 64 };
+
+int validate(const b200attn_params* p, int need) {
+  if (p == nullptr) return B200ATTN_EINVAL;
+  if (p->B <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->S <= 0 || !(p->scale > 0.f)) return B200ATTN_EINVAL;
+  if (p->d != kHeadDim) return B200ATTN_EHEADDIM;
+  if (p->Hq % p->Hkv != 0 || p->window < 0 || p->S > (1 << 24) || p->B > 65535 || p->Hq > 65535) return B200ATTN_ESHAPE;
+  if (p->sinks == nullptr || p->lse == nullptr) return B200ATTN_EINVAL;
+  if (!aligned16(p->lse)) return B200ATTN_EALIGN;
+  int rc;
+  if ((rc = check_tensor(p->q, p->B, p->Hq, p->S))) return rc;
+  if ((rc = check_tensor(p->k, p->B, p->Hkv, p->S))) return rc;
+  if ((rc = check_tensor(p->v, p->B, p->Hkv, p->S))) return rc;
+  if (need & (kNeedFwd | kNeedBwdIn))
+    if ((rc = check_tensor(p->o, p->B, p->Hq, p->S))) return rc;
+  if (need & kNeedBwdIn)
+    if ((rc = check_tensor(p->d_o, p->B, p->Hq, p->S))) return rc;
+  if (need & kNeedDelta) {
+    if (p->delta == nullptr) return B200ATTN_ESCRATCH;
+    if (!aligned16(p->delta)) return B200ATTN_EALIGN;
+  }
+  if ((need & kNeedPartial) && p->dsinks_partial == nullptr) return B200ATTN_ESCRATCH;
+  if ((need & kNeedDsinks) && p->dsinks == nullptr) return B200ATTN_EINVAL;
+  if (need & kNeedDq)
+    if ((rc = check_tensor(p->dq, p->B, p->Hq, p->S))) return rc;
+  if (need & kNeedDkv) {
+    if ((rc = check_tensor(p->dk, p->B, p->Hkv, p->S))) return rc;
+    if ((rc = check_tensor(p->dv, p->B, p->Hkv, p->S))) return rc;
+  }
+  return check_device(p->device);
+}
+
+KernelArgs make_args(const b200attn_params* p) {
+  KernelArgs a{};
+  a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.S = p->S;
+  a.S_pad = (int)b200attn_padded_len(p->S);
+  a.group = p->Hq / p->Hkv;
+  a.window = p->window;
+  a.scale = p->scale;
+  a.scale_log2 = p->scale * kLog2e;
+  a.seqlens = p->seqlens;
+  a.sinks = p->sinks;
+  a.status = p->status;
+  a.lse = p->lse;
+  a.delta = p->delta;
+  a.dsinks = p->dsinks;
+  a.dsinks_partial = p->dsinks_partial;
+  a.o = strided(p->o); a.d_o = strided(p->d_o); a.dq = strided(p->dq); a.dk = strided(p->dk); a.dv = strided(p->dv);
+  return a;
+}
+
+template <typename Kernel>
+int set_smem(Kernel kernel, size_t bytes) {
+  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess
+             ? B200ATTN_OK : B200ATTN_ECUDA;
+}
+
+int launch_status() { return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ECUDA; }
+
+}  // namespace
+
+extern "C" {
+
+int b200attn_version(void) { return B200ATTN_VERSION; }
+
+size_t b200attn_sizeof_params(void) { return sizeof(b200attn_params); }
+
+const char* b200attn_strerror(int code) {
+  switch (code) {
+    case B200ATTN_OK: return "success";
+    case B200ATTN_EINVAL: return "invalid argument (NULL pointer, non-positive size or scale)";
+    case B200ATTN_ESHAPE: return "unsupported shape (Hq % Hkv != 0, negative window, or size out of range)";
+    case B200ATTN_EHEADDIM: return "unsupported head_dim (only 64)";
+    case B200ATTN_EALIGN: return "pointer not 16-byte aligned or stride not a multiple of 8 elements";
+    case B200ATTN_EDEVICE: return "device is not an sm_100 (compute capability 10.x) GPU";
+    case B200ATTN_ECUDA: return "a CUDA runtime or driver call failed";
+    case B200ATTN_ETENSORMAP: return "the driver rejected a TMA tensor map";
+    case B200ATTN_ESCRATCH: return "scratch buffer missing";
+    default: return "unknown b200attn error code";
+  }
+}
+
+int64_t b200attn_padded_len(int64_t S) { return (S + B200ATTN_ROW_TILE - 1) / B200ATTN_ROW_TILE * B200ATTN_ROW_TILE; }
+
+int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p) {
+  if (p == nullptr) return 0;
+  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE);
+}
+
+int b200attn_fwd(const b200attn_params* p) {
+  int rc = validate(p, kNeedFwd);
+  if (rc) return rc;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  CUtensorMap tq, tk, tv;
+  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
+  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
+  const KernelArgs a = make_args(p);
+  const size_t smem = sizeof(FwdSmem) + 1024;
+  if ((rc = set_smem(attn_fwd_kernel, smem))) return rc;
+  dim3 grid(a.S_pad / kTile, p->Hq, p->B);
+  attn_fwd_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
+  return launch_status();
+}
+
+int b200attn_bwd_preprocess(const b200attn_params* p) {
+  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedPartial);
+  if (rc) return rc;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const KernelArgs a = make_args(p);
+  dim3 grid(a.S_pad / kTile, p->Hq, p->B);
+  attn_bwd_preprocess_kernel<<<grid, 128, 0, static_cast<cudaStream_t>(p->stream)>>>(a);
+  return launch_status();
+}
+
+int b200attn_bwd_dsinks(const b200attn_params* p) {
+  int rc = validate(p, kNeedPartial | kNeedDsinks);
+  if (rc) return rc;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const KernelArgs a = make_args(p);
+  attn_bwd_dsinks_kernel<<<p->Hq, 256, 0, static_cast<cudaStream_t>(p->stream)>>>(a);
+  return launch_status();
+}
+
+int b200attn_bwd_dkdv(const b200attn_params* p) {
+  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedDkv);
+  if (rc) return rc;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  CUtensorMap tq, tk, tv, tdo;
+  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
+  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
+  const KernelArgs a = make_args(p);
+  const size_t smem = sizeof(DkvSmem) + 1024;
+  if ((rc = set_smem(attn_bwd_dkdv_kernel, smem))) return rc;
+  dim3 grid(a.S_pad / kTile, p->Hkv, p->B);
+  attn_bwd_dkdv_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+  return launch_status();
+}
+
+int b200attn_bwd_dq(const b200attn_params* p) {
+  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedDq);
+  if (rc) return rc;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  CUtensorMap tq, tk, tv, tdo;
+  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
+  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
+  const KernelArgs a = make_args(p);
+  const size_t smem = sizeof(DqSmem) + 1024;
+  if ((rc = set_smem(attn_bwd_dq_kernel, smem))) return rc;
+  dim3 grid(a.S_pad / kTile, p->Hq, p->B);
+  attn_bwd_dq_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+  return launch_status();
+}
+
+int b200attn_bwd(const b200attn_params* p) {
+  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedPartial | kNeedDsinks | kNeedDq | kNeedDkv);
+  if (rc) return rc;
+  if ((rc = b200attn_bwd_preprocess(p))) return rc;
+  if ((rc = b200attn_bwd_dsinks(p))) return rc;
+  if ((rc = b200attn_bwd_dkdv(p))) return rc;
+  return b200attn_bwd_dq(p);
+}
+
+int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int32_t* status, int device, void* stream) {
+  if (a == nullptr || b == nullptr || d == nullptr || (mode != 0 && mode != 1)) return B200ATTN_EINVAL;
+  if (!aligned16(a) || !aligned16(b)) return B200ATTN_EALIGN;
+  int rc = check_device(device);
+  if (rc) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  CUtensorMap ta, tb;
+  // mode 0: A is (128 x 64), B is (128 x 64).  mode 1: A is read with plain loads, B is (128 x 64).
+  b200attn_tensor tb_view{const_cast<void*>(b), 128 * 64, 128 * 64, 64};
+  b200attn_tensor ta_view{const_cast<void*>(mode == 0 ? a : b), 128 * 64, 128 * 64, 64};
+  if ((rc = make_map(&ta, ta_view, 1, 1, 128, kTile))) return rc;
+  if ((rc = make_map(&tb, tb_view, 1, 1, 128, kTile))) return rc;
+  const size_t smem = sizeof(SelftestSmem) + 1024;
+  if ((rc = set_smem(umma_selftest_kernel, smem))) return rc;
+  umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, mode, static_cast<const __nv_bfloat16*>(a), d, status);
+  return launch_status();
+}
+
+}  // extern "C"

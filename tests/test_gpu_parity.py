@@ -1,0 +1,152 @@
+"""CUDA path vs the oracle and the reference-made golden fixtures.  All through the C ABI."""
+import ctypes
+
+import pytest
+import torch
+
+from conftest import GOLDEN_CASES, load_golden
+from gpu_util import (TOL_DSINKS, TOL_LSE, TOL_TENSOR, assert_close_valid, oracle_on_gpu, run_b200)
+from oracle import CONFIGS, AttnCase, make_inputs, rel_err
+from oregon_gpt_oss_patching_b200 import _cabi
+from oregon_gpt_oss_patching_b200.attention_kernel import attention, last_status
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.mark.parametrize("mode", [0, 1])
+def test_umma_building_blocks(mode):
+    lib = _cabi.load()
+    g = torch.Generator().manual_seed(mode)
+    a = torch.randn(128, 64 if mode == 0 else 128, generator=g).to(torch.bfloat16).to(DEV)
+    b = torch.randn(128, 64, generator=g).to(torch.bfloat16).to(DEV)
+    n = 128 if mode == 0 else 64
+    d = torch.full((128, n), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    rc = lib.b200attn_umma_selftest(mode, a.data_ptr(), b.data_ptr(), d.data_ptr(), status.data_ptr(), 0, None)
+    torch.cuda.synchronize()
+    assert rc == 0 and status.item() == 0
+    ref = a.float() @ (b.float().t() if mode == 0 else b.float())
+    assert rel_err(d, ref) < 1e-5
+
+
+@pytest.mark.parametrize("name", GOLDEN_CASES)
+def test_golden_fixture_parity(name):
+    g = load_golden(name)
+    q, k, v, do = (g[x].to(torch.bfloat16).to(DEV) for x in ("q", "k", "v", "do"))
+    res = run_b200(q, k, v, do, g["sinks"].to(DEV), g["scale"], g["window"], g["seqlens"])
+    lens = g["seqlens"] or [g["S"]] * g["B"]
+    ref = {key: g["hf_" + key] for key in ("o", "dq", "dk", "dv", "dsinks")}
+    assert_close_valid(res, ref, lens, g["S"])
+    assert last_status(DEV) == 0
+
+
+@pytest.mark.parametrize("name", ["full_s200_2kv", "pad_swa128"])
+def test_lse_and_delta_stage(name):
+    """Forward LSE vs the reference kernel's; preprocess stage delta vs rowsum(dO*O)."""
+    g = load_golden(name)
+    lib = _cabi.load()
+    q, k, v, do = (g[x].to(torch.bfloat16).to(DEV) for x in ("q", "k", "v", "do"))
+    B, Hq, S, d = q.shape
+    sinks = g["sinks"].to(DEV).float()
+    sl = torch.tensor(g["seqlens"], dtype=torch.int32, device=DEV) if g["seqlens"] else None
+    o = torch.empty(B, S, Hq, d, dtype=torch.bfloat16, device=DEV)
+    S_pad = _cabi.padded_len(S)
+    lse = torch.full((B, Hq, S_pad), float("nan"), device=DEV)
+    delta = torch.full((B, Hq, S_pad), float("nan"), device=DEV)
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    p = _cabi.Params()
+    p.B, p.Hq, p.Hkv, p.S, p.d, p.window, p.scale, p.device = B, Hq, k.shape[1], S, d, g["window"], g["scale"], 0
+    p.stream, p.status, p.sinks = None, status.data_ptr(), sinks.data_ptr()
+    p.seqlens = sl.data_ptr() if sl is not None else None
+    p.q, p.k, p.v = (_cabi.tensor4(t, "bhsd") for t in (q, k, v))
+    p.o, p.d_o, p.lse, p.delta = _cabi.tensor4(o, "bshd"), _cabi.tensor4(do, "bshd"), lse.data_ptr(), delta.data_ptr()
+    part = torch.empty(int(lib.b200attn_dsinks_scratch_floats(ctypes.byref(p))), device=DEV)
+    dsinks = torch.empty(Hq, device=DEV)
+    p.dsinks_partial, p.dsinks = part.data_ptr(), dsinks.data_ptr()
+    assert lib.b200attn_fwd(ctypes.byref(p)) == 0
+    assert lib.b200attn_bwd_preprocess(ctypes.byref(p)) == 0
+    assert lib.b200attn_bwd_dsinks(ctypes.byref(p)) == 0
+    torch.cuda.synchronize()
+    assert status.item() == 0
+    lens = g["seqlens"] or [S] * B
+    want_delta = (do.float() * o.float()).sum(-1).transpose(1, 2)  # (B,Hq,S)
+    for b, L in enumerate(lens):
+        assert rel_err(lse[b, :, :L], g["triton_lse"][b, :, :L]) < TOL_LSE
+        assert rel_err(delta[b, :, :L], want_delta[b, :, :L]) < 1e-5
+        assert float(delta[b, :, L:].abs().max() if L < S_pad else 0.0) == 0.0
+    assert rel_err(dsinks, g["hf_dsinks"]) < TOL_DSINKS
+
+
+@pytest.mark.parametrize("S,window,Hq,Hkv,B", [
+    (64, 0, 8, 1, 1), (1, 0, 2, 1, 1), (127, 0, 2, 2, 2), (129, 128, 8, 1, 1), (255, 64, 4, 2, 1),
+    (384, 128, 8, 1, 2), (640, 0, 16, 2, 1), (513, 256, 8, 4, 1), (1000, 128, 8, 1, 1), (300, 1, 2, 1, 1),
+])
+def test_odd_shapes_vs_oracle(S, window, Hq, Hkv, B):
+    case = AttnCase("t", B=B, S=S, Hq=Hq, Hkv=Hkv, window=window, seed=100 + S)
+    q, k, v, do, sinks = make_inputs(case, dtype=torch.bfloat16, device=DEV)
+    res = run_b200(q, k, v, do, sinks, case.scale, window)
+    ref = oracle_on_gpu(q, k, v, do, sinks, case.scale, window, row_block=256)
+    assert_close_valid(res, ref, [S] * B, S)
+    assert last_status(DEV) == 0
+
+
+@pytest.mark.parametrize("window", [0, 128])
+def test_ragged_padding(window):
+    lens = (700, 1, 129, 512)
+    case = AttnCase("t", B=4, S=768, Hq=8, Hkv=2, window=window, seqlens=lens, seed=7)
+    q, k, v, do, sinks = make_inputs(case, dtype=torch.bfloat16, device=DEV)
+    res = run_b200(q, k, v, do, sinks, case.scale, window, lens)
+    ref = oracle_on_gpu(q, k, v, do, sinks, case.scale, window, lens, row_block=256)
+    assert_close_valid(res, ref, lens, 768)
+    # gradient sent to padding rows must not matter
+    do2 = do.clone()
+    do2[1, 1:] = 3.0
+    res2 = run_b200(q, k, v, do2, sinks, case.scale, window, lens)
+    for key in res:
+        assert torch.equal(res[key], res2[key]), key
+
+
+def test_hf_strided_value_layout_and_bshd_views():
+    """V as HF hands it over with use_cache=False: a (B,S,Hkv,d) buffer viewed as (B,Hkv,S,d)."""
+    case = AttnCase("t", B=2, S=320, Hq=16, Hkv=2, window=128, seed=5)
+    q, k, v, do, sinks = make_inputs(case, dtype=torch.bfloat16, device=DEV)
+    v_strided = v.transpose(1, 2).contiguous().transpose(1, 2)
+    q_strided = q.transpose(1, 2).contiguous().transpose(1, 2)
+    assert not v_strided.is_contiguous()
+    a = run_b200(q, k, v, do, sinks, case.scale, 128)
+    b = run_b200(q_strided, k, v_strided, do, sinks, case.scale, 128)
+    for key in a:
+        assert torch.equal(a[key], b[key]), key
+    # dO arriving as a non-contiguous view
+    do_view = do.transpose(1, 2).contiguous().transpose(1, 2)
+    c = run_b200(q, k, v, do_view, sinks, case.scale, 128)
+    for key in a:
+        assert torch.equal(a[key], c[key]), key
+
+
+def test_bitwise_deterministic():
+    case = AttnCase("t", B=2, S=1024, Hq=16, Hkv=2, window=0, seed=9)
+    q, k, v, do, sinks = make_inputs(case, dtype=torch.bfloat16, device=DEV)
+    a = run_b200(q, k, v, do, sinks, case.scale, 0)
+    b = run_b200(q, k, v, do, sinks, case.scale, 0)
+    for key in a:
+        assert torch.equal(a[key], b[key]), key
+
+
+def test_cfg1_shape_bf16():
+    case = CONFIGS["cfg1"]
+    q, k, v, do, sinks = make_inputs(case, dtype=torch.bfloat16, device=DEV)
+    res = run_b200(q, k, v, do, sinks, case.scale, case.window)
+    ref = oracle_on_gpu(q, k, v, do, sinks, case.scale, case.window)
+    errs = assert_close_valid(res, ref, [case.S], case.S)
+    print("cfg1 errors", errs)
+
+
+def test_large_sink_and_extreme_logits_stay_finite():
+    case = AttnCase("t", B=1, S=256, Hq=4, Hkv=1, window=0, seed=3, input_scale=4.0)
+    q, k, v, do, _ = make_inputs(case, dtype=torch.bfloat16, device=DEV)
+    sinks = torch.tensor([60.0, -60.0, 0.0, 5.0], device=DEV)
+    res = run_b200(q, k, v, do, sinks, case.scale, 0)
+    ref = oracle_on_gpu(q, k, v, do, sinks, case.scale, 0)
+    assert_close_valid(res, ref, [256], 256)
