@@ -108,21 +108,21 @@ int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p);
 int b200attn_fwd(const b200attn_params* p);
 
 /*
- * Backward: dq, dk, dv, dsinks from q,k,v,o,lse,dO.  Enqueues, in order, the four stages
- * below.  Replaces attention_kernel.py:290-339 (dO transpose copy, zero-fills, the
+ * Backward: dq, dk, dv, dsinks from q,k,v,o,lse,dO.  Enqueues the four stages below in the
+ * order preprocess, dkdv, dq, dsinks.  Replaces attention_kernel.py:290-339 (dO transpose copy, zero-fills, the
  * `_attn_bwd_precompute_D` launch and the `_attn_bwd` launch).
  */
 int b200attn_bwd(const b200attn_params* p);
 
 /* Backward stages, exported separately so that each can be timed and tested alone. */
 
-/* delta = rowsum(dO * O) and per-block partial sums of -exp(sink - lse) * delta.
- * Replaces `_attn_bwd_precompute_D` (attention_kernel.py:102-120) and the dSinks part of
- * `_attn_bwd` (:173-176).  Writes delta, dsinks_partial. */
+/* delta = rowsum(dO * O).  Replaces `_attn_bwd_precompute_D` (attention_kernel.py:102-120).
+ * Reads o, dO; writes delta. */
 int b200attn_bwd_preprocess(const b200attn_params* p);
 
-/* dsinks[h] = sum of the partials (fixed order, warp-shuffle tree: deterministic, unlike the
- * reference's atomics at attention_kernel.py:176).  Reads dsinks_partial; writes dsinks. */
+/* dsinks[h] = sum of the per-warp partials the dq stage wrote (fixed order, warp-shuffle tree:
+ * deterministic, unlike the reference's atomics at attention_kernel.py:176).  Must run after
+ * b200attn_bwd_dq.  Reads dsinks_partial; writes dsinks. */
 int b200attn_bwd_dsinks(const b200attn_params* p);
 
 /* dk, dv: one CTA owns a 128-key tile of one KV head and loops over the query heads of the
@@ -130,7 +130,9 @@ int b200attn_bwd_dsinks(const b200attn_params* p);
  * global atomics, attention_kernel.py:201-212).  Reads q,k,v,dO,lse,delta. */
 int b200attn_bwd_dkdv(const b200attn_params* p);
 
-/* dq: one CTA owns a 128-row query tile of one head (attention_kernel.py:214-217). */
+/* dq: one CTA owns a 128-row query tile of one head (attention_kernel.py:214-217).  Also writes
+ * the sink-gradient partials -sum_i exp(sink - lse_i) * sum_j P_ij dP_ij of its rows
+ * (attention_kernel.py:173-175) to dsinks_partial.  Reads q,k,v,dO,lse,delta,sinks. */
 int b200attn_bwd_dq(const b200attn_params* p);
 
 /*

@@ -172,7 +172,7 @@ int64_t b200attn_padded_len(int64_t S) { return (S + B200ATTN_ROW_TILE - 1) / B2
 
 int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p) {
   if (p == nullptr) return 0;
-  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE);
+  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 4;
 }
 
 int b200attn_fwd(const b200attn_params* p) {
@@ -193,7 +193,7 @@ int b200attn_fwd(const b200attn_params* p) {
 }
 
 int b200attn_bwd_preprocess(const b200attn_params* p) {
-  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedPartial);
+  int rc = validate(p, kNeedBwdIn | kNeedDelta);
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
@@ -232,7 +232,7 @@ int b200attn_bwd_dkdv(const b200attn_params* p) {
 }
 
 int b200attn_bwd_dq(const b200attn_params* p) {
-  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedDq);
+  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedDq | kNeedPartial);
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
@@ -253,9 +253,9 @@ int b200attn_bwd(const b200attn_params* p) {
   int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedPartial | kNeedDsinks | kNeedDq | kNeedDkv);
   if (rc) return rc;
   if ((rc = b200attn_bwd_preprocess(p))) return rc;
-  if ((rc = b200attn_bwd_dsinks(p))) return rc;
   if ((rc = b200attn_bwd_dkdv(p))) return rc;
-  return b200attn_bwd_dq(p);
+  if ((rc = b200attn_bwd_dq(p))) return rc;
+  return b200attn_bwd_dsinks(p);
 }
 
 int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int32_t* status, int device, void* stream) {

@@ -9,6 +9,13 @@
 //     dQ += dS K          (accumulated in tensor memory over all key tiles)
 // and the epilogue stores dQ * scale.  This is the dq part of the reference's `_attn_bwd`
 // (attention_kernel.py:190-199, :206-207, :214-217).
+//
+// The same pass yields the sink gradient.  Because the softmax row (sink column included)
+// sums to one,  sum_j P_ij dP_ij  equals delta_i exactly, so each thread also accumulates that
+// sum in fp32 from the recomputed P and dP -- it does not inherit the bf16 rounding of the
+// stored O that delta = rowsum(dO*O) carries -- and the CTA writes, per warp,
+//     - sum_i exp(sink - LSE_i) * (sum_j P_ij dP_ij)
+// to the dSinks scratch (the reference's per-tile term, attention_kernel.py:173-175).
 #pragma once
 #include "attn_common.cuh"
 
@@ -48,8 +55,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int q0 = qt * kTile;
   const int len = seq_len(a, b);
 
-  if (q0 >= len) {  // padding only: dQ rows are zero
+  float* ds_partial = a.dsinks_partial + (((long long)h * a.B + b) * (a.S_pad / kTile) + qt) * 4;
+  if (q0 >= len) {  // padding only: dQ rows are zero, no sink gradient
     if (tid < kComputeThreads && q0 + tid < a.S) zero_row(a.dq.row(b, h, q0 + tid));
+    if (tid < 4) ds_partial[tid] = 0.f;
     return;
   }
 
@@ -149,6 +158,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
     const long long row_off = ((long long)(b * a.Hq + h)) * a.S_pad + i;
     const float neg_lse2 = -a.lse[row_off] * kLog2e;
     const float delta = a.delta[row_off];
+    float pdp = 0.f;  // sum_j P_ij dP_ij in fp32
     bool ok = true;
     uint32_t rs[32], rp[32];
 
@@ -171,6 +181,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
             if (!visible(i, kv0 + c * 32 + e, a.window, len)) p0 = 0.f;
             if (!visible(i, kv0 + c * 32 + e + 1, a.window, len)) p1 = 0.f;
           }
+          pdp = fmaf(p0, __uint_as_float(rp[e]), pdp);
+          pdp = fmaf(p1, __uint_as_float(rp[e + 1]), pdp);
           const float ds0 = p0 * (__uint_as_float(rp[e]) - delta);
           const float ds1 = p1 * (__uint_as_float(rp[e + 1]) - delta);
           pk[e >> 1] = pack_bf16(ds0, ds1);
@@ -185,6 +197,11 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
 
     if (ok) ok = warp_all(mbar_wait(bar_o, (nt - 1) & 1, abort_flag));
     if (ok) {
+      // sink gradient of this warp's 32 rows (fixed-order shuffle tree)
+      float dsk = (i < len) ? -fast_exp2(fmaf(a.sinks[h], kLog2e, neg_lse2)) * pdp : 0.f;
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) dsk += __shfl_xor_sync(0xffffffffu, dsk, off);
+      if (lane == 0) ds_partial[warp] = dsk;
       tc_fence_after_sync();
       uint32_t r0[32], r1[32];
       tmem_ld32(tmem_dq + lane_addr, r0);

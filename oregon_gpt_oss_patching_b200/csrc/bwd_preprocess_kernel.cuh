@@ -1,13 +1,11 @@
 // Memory-bound backward helpers.
 //
 // attn_bwd_preprocess_kernel:  delta[b,h,i] = sum_c dO[b,h,i,c] * O[b,h,i,c]  in fp32 (the
-// reference's `_attn_bwd_precompute_D`, attention_kernel.py:102-120) and, in the same pass,
-// one partial sum per 128-row block of  -exp(sink_h - lse[b,h,i]) * delta[b,h,i]  (the
-// reference's per-tile dSinks term, attention_kernel.py:173-175).
+// reference's `_attn_bwd_precompute_D`, attention_kernel.py:102-120).
 //
-// attn_bwd_dsinks_kernel:  dsinks[h] = sum of head h's partials, in a fixed order with a
-// warp-shuffle tree, so the result is bit-reproducible (the reference adds its partials with
-// relaxed atomics, attention_kernel.py:176).
+// attn_bwd_dsinks_kernel:  dsinks[h] = sum of head h's per-warp partials written by the dQ
+// kernel, in a fixed order with a warp-shuffle tree, so the result is bit-reproducible (the
+// reference adds its per-tile terms with relaxed atomics, attention_kernel.py:176).
 #pragma once
 #include "attn_common.cuh"
 
@@ -36,7 +34,6 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
   const int sub = lane >> 3;       // row within the step
   const int part = lane & 7;       // 16-byte slice of the row
   const long long row_base = ((long long)(b * a.Hq + h)) * a.S_pad + (long long)tile * kTile;
-  const float sink = a.sinks[h];
 
   uint4 xo[8], xd[8];
 #pragma unroll
@@ -50,7 +47,6 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
       xd[step] = make_uint4(0, 0, 0, 0);
     }
   }
-  float ds_part = 0.f;
 #pragma unroll
   for (int step = 0; step < 8; ++step) {
     float s = dot8_bf16(xo[step], xd[step]);
@@ -58,21 +54,7 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     s += __shfl_xor_sync(0xffffffffu, s, 4);
     const int r = warp * 32 + step * 4 + sub;
-    const int i = tile * kTile + r;
-    if (part == 0) {
-      a.delta[row_base + r] = s;  // zero for padding rows
-      if (i < len) ds_part -= __expf(sink - a.lse[row_base + r]) * s;
-    }
-  }
-  // block partial: lanes, then warps, in a fixed order
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) ds_part += __shfl_xor_sync(0xffffffffu, ds_part, off);
-  __shared__ float warp_sum[4];
-  if (lane == 0) warp_sum[warp] = ds_part;
-  __syncthreads();
-  if (tid == 0) {
-    const int ntiles = a.S_pad / kTile;
-    a.dsinks_partial[((long long)h * a.B + b) * ntiles + tile] = (warp_sum[0] + warp_sum[1]) + (warp_sum[2] + warp_sum[3]);
+    if (part == 0) a.delta[row_base + r] = s;  // zero for padding rows
   }
 }
 
@@ -80,7 +62,7 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
 __global__ void __launch_bounds__(256) attn_bwd_dsinks_kernel(const KernelArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x;
-  const int n = a.B * (a.S_pad / kTile);
+  const int n = a.B * (a.S_pad / kTile) * 4;  // four warp partials per query tile
   const float* src = a.dsinks_partial + (long long)h * n;
   float s = 0.f;
   for (int idx = tid; idx < n; idx += 256) s += src[idx];

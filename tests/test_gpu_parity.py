@@ -64,8 +64,11 @@ def test_lse_and_delta_stage(name):
     part = torch.empty(int(lib.b200attn_dsinks_scratch_floats(ctypes.byref(p))), device=DEV)
     dsinks = torch.empty(Hq, device=DEV)
     p.dsinks_partial, p.dsinks = part.data_ptr(), dsinks.data_ptr()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    p.dq, p.dk, p.dv = (_cabi.tensor4(t, "bhsd") for t in (dq, dk, dv))
     assert lib.b200attn_fwd(ctypes.byref(p)) == 0
     assert lib.b200attn_bwd_preprocess(ctypes.byref(p)) == 0
+    assert lib.b200attn_bwd_dq(ctypes.byref(p)) == 0
     assert lib.b200attn_bwd_dsinks(ctypes.byref(p)) == 0
     torch.cuda.synchronize()
     assert status.item() == 0
