@@ -187,8 +187,9 @@ int b200attn_fwd(const b200attn_params* p) {
   const KernelArgs a = make_args(p);
   const size_t smem = sizeof(FwdSmem) + 1024;
   if ((rc = set_smem(attn_fwd_kernel, smem))) return rc;
-  dim3 grid(a.S_pad / kTile, p->Hq, p->B);
-  attn_fwd_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
+  const int heads_per_cta = (a.group % 2 == 0) ? 2 : 1;  // two heads of a KV group share staged K/V tiles
+  dim3 grid(a.S_pad / kTile, p->Hq / heads_per_cta, p->B);
+  attn_fwd_kernel<<<grid, kFwdThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
   return launch_status();
 }
 

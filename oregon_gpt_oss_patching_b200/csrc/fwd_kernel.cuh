@@ -1,41 +1,115 @@
 // Forward attention kernel for sm_100a.
 //
-// One CTA = one 128-row query tile of one query head of one sequence.  Per visible
-// 128-key tile:  S = Q K^T on tcgen05 (operands staged by TMA, accumulator in tensor
-// memory), online softmax in registers with one thread per row (running max starts at the
-// head's sink logit, the sink joins the denominator in the epilogue), P written back to
-// tensor memory as bf16 and used as the A operand of  O_tile = P V.  Key tiles that are
-// entirely masked (above the diagonal, left of the window, past the sequence end) are
-// never loaded.  Computes what the reference's `_attn_fwd` does
-// (attention_kernel.py:11-100), in the log2 domain.
+// One CTA = one 128-row query tile of TWO query heads of the same KV group (tile A and tile
+// B), so that every K/V tile staged in shared memory by TMA feeds two heads; the other heads
+// of the group run in neighbouring CTAs and find the same K/V tiles in L2.  (With an odd group
+// size only tile A is active.)  Per visible 128-key tile and per query tile:
+//     S = Q K^T                      tcgen05.mma, fp32 accumulator in tensor memory
+//     P = 2^(S*scale*log2e - m)      one thread per row, online softmax in registers
+//     O_tile = P V                   tcgen05.mma with P (bf16) as the A operand from tensor memory
+//     acc = acc * alpha + O_tile     in registers
+// The running maximum m starts at the head's sink logit; the sink joins the denominator in the
+// epilogue and carries no value.  Computes what the reference's `_attn_fwd` does
+// (attention_kernel.py:11-100), in the log2 domain.  Key tiles that are entirely masked (above
+// the diagonal, left of the window, past the sequence end) are never loaded.
 //
-// Warps 0-3: softmax + output accumulation (thread r owns row r = TMEM lane r).
-// Warp 4, lane 0: TMA producer and MMA issuer.
-// Two CTAs fit per SM (256 TMEM columns, 80 KB shared memory each), so one CTA's tensor
-// work overlaps the other's softmax.
+// Warp roles: warps 0-3 softmax of tile A, warps 4-7 softmax of tile B (thread r owns row r =
+// TMEM lane r), warp 8 lane 0 issues every MMA, warp 9 lane 0 issues every TMA load.  While one
+// tile's threads run their softmax the tensor core works for the other tile.
+//
+// The softmax is single-pass: it exponentiates against the running maximum it already has and
+// only if some row of the warp grew by more than 2^8 re-reads S and redoes the tile with the
+// updated maximum (rare after the first tile), which halves the tensor-memory reads.
 #pragma once
 #include "attn_common.cuh"
 
 namespace b200attn {
 
-constexpr int kFwdStages = 2;
-constexpr int kFwdTmemCols = 256;  // S: [0,128)  P: [128,192)  O tile: [192,256)
+constexpr int kFwdStages = 3;
+constexpr int kFwdThreads = 320;
+constexpr int kFwdTmemCols = 512;
+// tensor-memory columns: S_A [0,128) S_B [128,256) P_A [256,320) P_B [320,384) O_A [384,448) O_B [448,512)
+constexpr float kRescaleThreshold = 8.f;
 
 struct FwdSmem {
-  alignas(1024) uint8_t q[kTileBytes];
+  alignas(1024) uint8_t q[2][kTileBytes];
   alignas(1024) uint8_t k[kFwdStages][kTileBytes];
   alignas(1024) uint8_t v[kFwdStages][kTileBytes];
   alignas(8) uint64_t bar_q;
-  uint64_t bar_k[kFwdStages];
-  uint64_t bar_v[kFwdStages];
-  uint64_t bar_s;  // S ready in TMEM            (tcgen05.commit)
-  uint64_t bar_p;  // P written by 128 threads   (count 128)
-  uint64_t bar_o;  // O tile ready in TMEM       (tcgen05.commit)
+  uint64_t bar_kv_full[kFwdStages];
+  uint64_t bar_kv_empty[kFwdStages];
+  uint64_t bar_s_full[2];   // S of tile X ready            (tcgen05.commit)
+  uint64_t bar_p_full[2];   // P of tile X written          (128 arrivals)
+  uint64_t bar_o_full[2];   // O_tile of tile X ready       (tcgen05.commit)
+  uint64_t bar_o_empty[2];  // O_tile of tile X consumed    (128 arrivals)
   uint32_t tmem_base;
   int abort_flag;
+  int loads_issued;         // K/V tile loads the loader has issued so far (for the abort drain)
 };
 
-__global__ void __launch_bounds__(kThreads, 2)
+// acc = acc * alpha + O_tile for the 64 output columns of this thread's row
+__device__ __forceinline__ void fwd_accumulate(float (&acc)[kHeadDim], uint32_t tmem_o_row, float alpha) {
+  uint32_t r0[32], r1[32];
+  tmem_ld32(tmem_o_row, r0);
+  tmem_ld32(tmem_o_row + 32, r1);
+  tmem_wait_ld();
+  if (alpha == 1.f) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      acc[e] += __uint_as_float(r0[e]);
+      acc[32 + e] += __uint_as_float(r1[e]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      acc[e] = fmaf(acc[e], alpha, __uint_as_float(r0[e]));
+      acc[32 + e] = fmaf(acc[32 + e], alpha, __uint_as_float(r1[e]));
+    }
+  }
+}
+
+// One 32-column chunk of the softmax: p = 2^(s*scale - m), optional mask, row sum, running
+// maximum of the exponent, bf16 pack and store into the P columns.
+template <bool kMask>
+__device__ __forceinline__ void fwd_softmax_chunk(const uint32_t (&r)[32], uint32_t tmem_p_chunk, float scale_log2,
+                                                  float m, int i, int j0, int window, int len, float& mx,
+                                                  float& rowsum) {
+  uint32_t pk[16];
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float x0 = fmaf(__uint_as_float(r[e]), scale_log2, -m);
+    float x1 = fmaf(__uint_as_float(r[e + 1]), scale_log2, -m);
+    if (kMask) {
+      if (!visible(i, j0 + e, window, len)) x0 = -INFINITY;
+      if (!visible(i, j0 + e + 1, window, len)) x1 = -INFINITY;
+    }
+    mx = fmaxf(mx, fmaxf(x0, x1));
+    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
+    rowsum += p0 + p1;
+    pk[e >> 1] = pack_bf16(p0, p1);
+  }
+  tmem_st16(tmem_p_chunk, pk);
+}
+
+template <bool kMask>
+__device__ __forceinline__ void fwd_softmax_pass(uint32_t tmem_s_row, uint32_t tmem_p_row, float scale_log2, float m,
+                                                 int i, int kv0, int window, int len, float& mx, float& rowsum) {
+  uint32_t ra[32], rb[32];
+  tmem_ld32(tmem_s_row, ra);
+  tmem_wait_ld();
+  tmem_ld32(tmem_s_row + 32, rb);
+  fwd_softmax_chunk<kMask>(ra, tmem_p_row, scale_log2, m, i, kv0, window, len, mx, rowsum);
+  tmem_wait_ld();
+  tmem_ld32(tmem_s_row + 64, ra);
+  fwd_softmax_chunk<kMask>(rb, tmem_p_row + 16, scale_log2, m, i, kv0 + 32, window, len, mx, rowsum);
+  tmem_wait_ld();
+  tmem_ld32(tmem_s_row + 96, rb);
+  fwd_softmax_chunk<kMask>(ra, tmem_p_row + 32, scale_log2, m, i, kv0 + 64, window, len, mx, rowsum);
+  tmem_wait_ld();
+  fwd_softmax_chunk<kMask>(rb, tmem_p_row + 48, scale_log2, m, i, kv0 + 96, window, len, mx, rowsum);
+}
+
+__global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -45,43 +119,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int warp = tid >> 5;
   const int lane = tid & 31;
   const int b = blockIdx.z;
-  const int h = blockIdx.y;
-  const int g = h / a.group;
-  const int qt = gridDim.x - 1 - blockIdx.x;  // long (late) tiles first
+  const int n_act = (a.group % 2 == 0) ? 2 : 1;   // query heads (tiles) handled by this CTA
+  const int h0 = blockIdx.y * n_act;
+  const int g = h0 / a.group;
+  const int qt = gridDim.x - 1 - blockIdx.x;      // long (late) tiles first
   const int q0 = qt * kTile;
   const int len = seq_len(a, b);
-  float* lse_row = a.lse + ((long long)(b * a.Hq + h)) * a.S_pad + q0;
 
   if (q0 >= len) {  // tile is padding only: define its output, no tensor work
-    if (tid < kComputeThreads) {
-      if (q0 + tid < a.S) zero_row(a.o.row(b, h, q0 + tid));
-      lse_row[tid] = 0.f;
+    if (tid < n_act * kComputeThreads) {
+      const int x = tid >> 7, r = tid & 127;
+      if (q0 + r < a.S) zero_row(a.o.row(b, h0 + x, q0 + r));
+      a.lse[((long long)(b * a.Hq + h0 + x)) * a.S_pad + q0 + r] = 0.f;
     }
     return;
   }
 
-  const int hi = min(q0 + kTile - 1, len - 1);                         // last visible key
-  const int lo = a.window ? max(0, q0 - a.window + 1) : 0;             // first visible key
+  const int hi = min(q0 + kTile - 1, len - 1);              // last visible key
+  const int lo = a.window ? max(0, q0 - a.window + 1) : 0;  // first visible key
   const int t_first = lo / kTile;
   const int nt = hi / kTile - t_first + 1;
 
-  const uint32_t bar_q = smem_u32(&sm->bar_q), bar_s = smem_u32(&sm->bar_s), bar_p = smem_u32(&sm->bar_p),
-                 bar_o = smem_u32(&sm->bar_o);
+  const uint32_t bar_q = smem_u32(&sm->bar_q);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
     mbar_init(bar_q, 1);
     for (int s = 0; s < kFwdStages; ++s) {
-      mbar_init(smem_u32(&sm->bar_k[s]), 1);
-      mbar_init(smem_u32(&sm->bar_v[s]), 1);
+      mbar_init(smem_u32(&sm->bar_kv_full[s]), 1);
+      mbar_init(smem_u32(&sm->bar_kv_empty[s]), 1);
     }
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, kComputeThreads);
-    mbar_init(bar_o, 1);
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(smem_u32(&sm->bar_s_full[x]), 1);
+      mbar_init(smem_u32(&sm->bar_p_full[x]), kComputeThreads);
+      mbar_init(smem_u32(&sm->bar_o_full[x]), 1);
+      mbar_init(smem_u32(&sm->bar_o_empty[x]), kComputeThreads);
+    }
     sm->abort_flag = 0;
+    sm->loads_issued = 0;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
     tmem_alloc(smem_u32(&sm->tmem_base), kFwdTmemCols);
     tmem_relinquish();
@@ -90,146 +168,138 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_p = tmem + 128, tmem_o = tmem + 192;
 
-  if (warp == 4) {
-    // ------------------------------ producer + MMA issuer ------------------------------
+  if (warp == 9) {
+    // ------------------------------------ TMA loader ------------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
-      mbar_arrive_expect_tx(bar_q, kTileBytes);
-      tma_load_4d(smem_u32(sm->q), &tm_q, bar_q, 0, q0, h, b);
-      const int pre = nt < kFwdStages ? nt : kFwdStages;
-      for (int s = 0; s < pre; ++s) {
-        const int kv0 = (t_first + s) * kTile;
-        mbar_arrive_expect_tx(smem_u32(&sm->bar_k[s]), kTileBytes);
-        tma_load_4d(smem_u32(sm->k[s]), &tm_k, smem_u32(&sm->bar_k[s]), 0, kv0, g, b);
-        mbar_arrive_expect_tx(smem_u32(&sm->bar_v[s]), kTileBytes);
-        tma_load_4d(smem_u32(sm->v[s]), &tm_v, smem_u32(&sm->bar_v[s]), 0, kv0, g, b);
-      }
-      const uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, 0, 0);
-      const uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, 0, 1);
-      const uint64_t dq_desc = desc_kmajor(smem_u32(sm->q));
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
-      int issued = pre, k_waited = 0, v_waited = 0;  // K/V tile loads issued / seen complete
-      for (int t = 0; ok && t < nt; ++t) {
+      mbar_arrive_expect_tx(bar_q, n_act * kTileBytes);
+      for (int x = 0; x < n_act; ++x) tma_load_4d(smem_u32(sm->q[x]), &tm_q, bar_q, 0, q0, h0 + x, b);
+      for (int t = 0; t < nt; ++t) {
         const int s = t % kFwdStages;
-        const uint32_t ph = (t / kFwdStages) & 1;
-        // S = Q K^T
-        if (!(ok = mbar_wait(smem_u32(&sm->bar_k[s]), ph, abort_flag))) break;
-        k_waited = t + 1;
-        tc_fence_after_sync();
-        const uint64_t dk_desc = desc_kmajor(smem_u32(sm->k[s]));
-#pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          umma_ss(tmem_s, dq_desc + kk * kDescKStepKMajor, dk_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
-        umma_commit(bar_s);
-        // O_tile = P V   (P from tensor memory)
-        if (!(ok = mbar_wait(smem_u32(&sm->bar_v[s]), ph, abort_flag))) break;
-        v_waited = t + 1;
-        if (!(ok = mbar_wait(bar_p, t & 1, abort_flag))) break;
-        tc_fence_after_sync();
-        const uint64_t dv_desc = desc_mnmajor(smem_u32(sm->v[s]));
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem_o, tmem_p + kk * 8, dv_desc + kk * kDescKStepMNMajor, idesc_pv, kk > 0);
-        umma_commit(bar_o);
-        // refill this stage once the tensor core is done with it
-        if (t + kFwdStages < nt) {
-          if (!(ok = mbar_wait(bar_o, t & 1, abort_flag))) break;
-          const int kv0 = (t_first + t + kFwdStages) * kTile;
-          mbar_arrive_expect_tx(smem_u32(&sm->bar_k[s]), kTileBytes);
-          tma_load_4d(smem_u32(sm->k[s]), &tm_k, smem_u32(&sm->bar_k[s]), 0, kv0, g, b);
-          mbar_arrive_expect_tx(smem_u32(&sm->bar_v[s]), kTileBytes);
-          tma_load_4d(smem_u32(sm->v[s]), &tm_v, smem_u32(&sm->bar_v[s]), 0, kv0, g, b);
-          ++issued;
+        if (t >= kFwdStages && !mbar_wait(smem_u32(&sm->bar_kv_empty[s]), ((t / kFwdStages) - 1) & 1, abort_flag)) {
+          report_abort(a);
+          break;
         }
-      }
-      if (!ok) {
-        report_abort(a);
-        // give copies that are still in flight a bounded chance to land before the CTA exits
-        for (int t = k_waited; t < issued; ++t)
-          mbar_wait_drain(smem_u32(&sm->bar_k[t % kFwdStages]), (t / kFwdStages) & 1);
-        for (int t = v_waited; t < issued; ++t)
-          mbar_wait_drain(smem_u32(&sm->bar_v[t % kFwdStages]), (t / kFwdStages) & 1);
+        const int kv0 = (t_first + t) * kTile;
+        const uint32_t bar = smem_u32(&sm->bar_kv_full[s]);
+        mbar_arrive_expect_tx(bar, 2 * kTileBytes);
+        tma_load_4d(smem_u32(sm->k[s]), &tm_k, bar, 0, kv0, g, b);
+        tma_load_4d(smem_u32(sm->v[s]), &tm_v, bar, 0, kv0, g, b);
+        *reinterpret_cast<volatile int*>(&sm->loads_issued) = t + 1;
       }
     }
     __syncwarp();
-  } else {
-    // ------------------------------------ softmax ------------------------------------
-    const int i = q0 + tid;                               // this thread's query position
-    const uint32_t lane_addr = uint32_t(warp * 32) << 16;  // this warp's TMEM lane quarter
+  } else if (warp == 8) {
+    // ------------------------------------ MMA issuer ------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, 0, 1);
+      uint64_t q_desc[2];
+      for (int x = 0; x < 2; ++x) q_desc[x] = desc_kmajor(smem_u32(sm->q[x]));
+      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      if (ok) ok = mbar_wait(smem_u32(&sm->bar_kv_full[0]), 0, abort_flag);
+      if (ok) {
+        tc_fence_after_sync();
+        const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[0]));
+        for (int x = 0; x < n_act; ++x) {
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)
+            umma_ss(tmem + x * 128, q_desc[x] + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
+          umma_commit(smem_u32(&sm->bar_s_full[x]));
+        }
+      }
+      for (int t = 0; ok && t < nt; ++t) {
+        const int s = t % kFwdStages;
+        const int sn = (t + 1) % kFwdStages;
+        if (t + 1 < nt && !(ok = mbar_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1, abort_flag))) break;
+        const uint64_t kn_desc = desc_kmajor(smem_u32(sm->k[sn]));
+        const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
+        for (int x = 0; ok && x < n_act; ++x) {
+          if (!(ok = mbar_wait(smem_u32(&sm->bar_p_full[x]), t & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          if (t >= 1) {
+            if (!(ok = mbar_wait(smem_u32(&sm->bar_o_empty[x]), (t - 1) & 1, abort_flag))) break;
+            tc_fence_after_sync();
+          }
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ts(tmem + 384 + x * 64, tmem + 256 + x * 64 + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, kk > 0);
+          umma_commit(smem_u32(&sm->bar_o_full[x]));
+          // S of the next key tile goes behind P V in the pipe: when it is ready, P has been read
+          // and the softmax threads may overwrite the P columns.
+          if (t + 1 < nt) {
+#pragma unroll
+            for (int kk = 0; kk < kHeadDim / 16; ++kk)
+              umma_ss(tmem + x * 128, q_desc[x] + kk * kDescKStepKMajor, kn_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
+            umma_commit(smem_u32(&sm->bar_s_full[x]));
+          }
+        }
+        if (ok) umma_commit(smem_u32(&sm->bar_kv_empty[s]));  // K[s], V[s] are free once these MMAs retire
+      }
+      if (!ok) report_abort(a);
+    }
+    __syncwarp();
+  } else if (warp < 4 * n_act) {
+    // -------------------------------------- softmax --------------------------------------
+    const int x = warp >> 2;                                      // tile A or B
+    const int h = h0 + x;
+    const int r = tid & 127;
+    const int i = q0 + r;                                         // this thread's query position
+    const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;   // this warp's TMEM lane quarter
+    const uint32_t tmem_s_row = tmem + x * 128 + lane_addr;
+    const uint32_t tmem_p_row = tmem + 256 + x * 64 + lane_addr;
+    const uint32_t tmem_o_row = tmem + 384 + x * 64 + lane_addr;
+    const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_p = smem_u32(&sm->bar_p_full[x]),
+                   bar_o = smem_u32(&sm->bar_o_full[x]), bar_oe = smem_u32(&sm->bar_o_empty[x]);
     const float sink2 = a.sinks[h] * kLog2e;
-    float m = sink2;   // running max (log2 domain), starts at the sink logit
-    float l = 0.f;     // running denominator without the sink
+    float m = sink2;         // reference maximum of the exponents (log2 domain), starts at the sink logit
+    float l = 0.f;           // running denominator without the sink, relative to m
+    float alpha = 1.f;       // rescale factor of the latest key tile
     float acc[kHeadDim];
 #pragma unroll
     for (int c = 0; c < kHeadDim; ++c) acc[c] = 0.f;
     bool ok = true;
-    uint32_t r[32];
 
     for (int t = 0; t < nt; ++t) {
       const int kv0 = (t_first + t) * kTile;
       const bool need_mask = tile_needs_mask(q0, kv0, a.window, len);
       if (!(ok = warp_all(mbar_wait(bar_s, t & 1, abort_flag)))) break;
-      tc_fence_after_sync();
-      // pass 1: row maximum of the visible logits
-      float mx = -INFINITY;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(tmem_s + lane_addr + c * 32, r);
-        tmem_wait_ld();
-        if (need_mask) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e)
-            if (visible(i, kv0 + c * 32 + e, a.window, len)) mx = fmaxf(mx, __uint_as_float(r[e]));
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(r[e]));
-        }
+      if (t > 0) {
+        // P V of the previous key tile retired before this S did: fold it in first
+        if (!(ok = warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag)))) break;
+        tc_fence_after_sync();
+        fwd_accumulate(acc, tmem_o_row, alpha);
+        tc_fence_before_sync();
+        mbar_arrive(bar_oe);
       }
-      const float m_new = fmaxf(m, mx * a.scale_log2);
-      const float alpha = fast_exp2(m - m_new);
-      // pass 2: p = 2^(s*scale - m), row sum, P -> TMEM as bf16
-      float rowsum = 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(tmem_s + lane_addr + c * 32, r);
-        tmem_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(r[e]), a.scale_log2, -m_new));
-          float p1 = fast_exp2(fmaf(__uint_as_float(r[e + 1]), a.scale_log2, -m_new));
-          if (need_mask) {
-            if (!visible(i, kv0 + c * 32 + e, a.window, len)) p0 = 0.f;
-            if (!visible(i, kv0 + c * 32 + e + 1, a.window, len)) p1 = 0.f;
-          }
-          rowsum += p0 + p1;
-          pk[e >> 1] = pack_bf16(p0, p1);
-        }
-        tmem_st16(tmem_p + lane_addr + c * 16, pk);
+      tc_fence_after_sync();
+      float mx = -INFINITY, rowsum = 0.f;
+      if (need_mask) fwd_softmax_pass<true>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
+      else fwd_softmax_pass<false>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
+      alpha = 1.f;
+      if (__any_sync(0xffffffffu, mx > kRescaleThreshold)) {
+        // some row outgrew the reference maximum: move it up and redo this tile
+        const float m_new = m + fmaxf(mx, 0.f);
+        alpha = fast_exp2(m - m_new);
+        m = m_new;
+        mx = -INFINITY;
+        rowsum = 0.f;
+        tmem_wait_st();
+        if (need_mask) fwd_softmax_pass<true>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
+        else fwd_softmax_pass<false>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
       }
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar_p);
       l = l * alpha + rowsum;
-      m = m_new;
-      // O += P V
-      if (!(ok = warp_all(mbar_wait(bar_o, t & 1, abort_flag)))) break;
-      tc_fence_after_sync();
-#pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        tmem_ld32(tmem_o + lane_addr + c * 32, r);
-        tmem_wait_ld();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) acc[c * 32 + e] = fmaf(acc[c * 32 + e], alpha, __uint_as_float(r[e]));
-      }
-      tc_fence_before_sync();
     }
-
+    if (ok) ok = warp_all(mbar_wait(bar_o, (nt - 1) & 1, abort_flag));
     if (ok) {
+      tc_fence_after_sync();
+      fwd_accumulate(acc, tmem_o_row, alpha);
       const float z = l + fast_exp2(sink2 - m);   // the sink joins the denominator only
       const float inv = 1.f / z;
       if (i < a.S) {
@@ -239,15 +309,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           store_bf16x8(dst + c, pack_bf16(acc[c] * inv, acc[c + 1] * inv), pack_bf16(acc[c + 2] * inv, acc[c + 3] * inv),
                        pack_bf16(acc[c + 4] * inv, acc[c + 5] * inv), pack_bf16(acc[c + 6] * inv, acc[c + 7] * inv));
       }
-      lse_row[tid] = (i < len) ? (m + log2f(z)) * kLn2 : 0.f;
+      a.lse[((long long)(b * a.Hq + h)) * a.S_pad + i] = (i < len) ? (m + log2f(z)) * kLn2 : 0.f;
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
     tmem_dealloc(tmem, kFwdTmemCols);
+  }
+  if (sm->abort_flag && tid == 9 * 32) {
+    // abandoned: give copies still in flight a bounded chance to land before shared memory goes away
+    const int issued = sm->loads_issued;
+    mbar_wait_drain(bar_q, 0);
+    for (int t = max(0, issued - kFwdStages); t < issued; ++t)
+      mbar_wait_drain(smem_u32(&sm->bar_kv_full[t % kFwdStages]), (t / kFwdStages) & 1);
   }
 }
 
