@@ -17,19 +17,20 @@
 // TMEM lane r), warp 8 lane 0 issues every MMA, warp 9 lane 0 issues every TMA load.  While one
 // tile's threads run their softmax the tensor core works for the other tile.
 //
-// The softmax is single-pass: it exponentiates against the running maximum it already has and
-// only if some row of the warp grew by more than 2^8 re-reads S and redoes the tile with the
-// updated maximum (rare after the first tile), which halves the tensor-memory reads.
+// A softmax thread holds its whole 128-column row of S in registers (one burst of tensor-memory
+// loads per tile), so the row maximum, the exponentials and the row sum are computed without a
+// second read.  The register file is re-partitioned with setmaxnreg: the two softmax warpgroups
+// take 224 registers per thread, the warpgroup holding the MMA and TMA warps keeps 56
+// (2*128*224 + 128*56 = 384*168, the pool the CTA is launched with).
 #pragma once
 #include "attn_common.cuh"
 
 namespace b200attn {
 
 constexpr int kFwdStages = 3;
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax A, softmax B, {MMA warp, TMA warp, 2 idle warps}
 constexpr int kFwdTmemCols = 512;
 // tensor-memory columns: S_A [0,128) S_B [128,256) P_A [256,320) P_B [320,384) O_A [384,448) O_B [448,512)
-constexpr float kRescaleThreshold = 8.f;
 
 struct FwdSmem {
   alignas(1024) uint8_t q[2][kTileBytes];
@@ -68,46 +69,47 @@ __device__ __forceinline__ void fwd_accumulate(float (&acc)[kHeadDim], uint32_t 
   }
 }
 
-// One 32-column chunk of the softmax: p = 2^(s*scale - m), optional mask, row sum, running
-// maximum of the exponent, bf16 pack and store into the P columns.
+// Softmax of one 128-column row held in registers: returns the new running maximum, writes
+// P (bf16) to tensor memory and adds the row sum.
 template <bool kMask>
-__device__ __forceinline__ void fwd_softmax_chunk(const uint32_t (&r)[32], uint32_t tmem_p_chunk, float scale_log2,
-                                                  float m, int i, int j0, int window, int len, float& mx,
-                                                  float& rowsum) {
-  uint32_t pk[16];
+__device__ __forceinline__ float fwd_softmax_row(uint32_t tmem_s_row, uint32_t tmem_p_row, float scale_log2, float m,
+                                                 int i, int kv0, int window, int len, float& rowsum) {
+  uint32_t s[4][32];
 #pragma unroll
-  for (int e = 0; e < 32; e += 2) {
-    float x0 = fmaf(__uint_as_float(r[e]), scale_log2, -m);
-    float x1 = fmaf(__uint_as_float(r[e + 1]), scale_log2, -m);
-    if (kMask) {
-      if (!visible(i, j0 + e, window, len)) x0 = -INFINITY;
-      if (!visible(i, j0 + e + 1, window, len)) x1 = -INFINITY;
-    }
-    mx = fmaxf(mx, fmaxf(x0, x1));
-    const float p0 = fast_exp2(x0), p1 = fast_exp2(x1);
-    rowsum += p0 + p1;
-    pk[e >> 1] = pack_bf16(p0, p1);
+  for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s_row + c * 32, s[c]);
+  tmem_wait_ld();
+  if (kMask) {
+#pragma unroll
+    for (int c = 0; c < 4; ++c)
+#pragma unroll
+      for (int e = 0; e < 32; ++e)
+        if (!visible(i, kv0 + c * 32 + e, window, len)) s[c][e] = 0xff800000u;  // -inf
   }
-  tmem_st16(tmem_p_chunk, pk);
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(s[c][e]));
+  const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2);
+  float sum[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][e]), scale_log2, -m_new));
+      const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][e + 1]), scale_log2, -m_new));
+      sum[(e >> 1) & 3] += p0 + p1;
+      pk[e >> 1] = pack_bf16(p0, p1);
+    }
+    tmem_st16(tmem_p_row + c * 16, pk);
+  }
+  rowsum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
+  return m_new;
 }
 
-template <bool kMask>
-__device__ __forceinline__ void fwd_softmax_pass(uint32_t tmem_s_row, uint32_t tmem_p_row, float scale_log2, float m,
-                                                 int i, int kv0, int window, int len, float& mx, float& rowsum) {
-  uint32_t ra[32], rb[32];
-  tmem_ld32(tmem_s_row, ra);
-  tmem_wait_ld();
-  tmem_ld32(tmem_s_row + 32, rb);
-  fwd_softmax_chunk<kMask>(ra, tmem_p_row, scale_log2, m, i, kv0, window, len, mx, rowsum);
-  tmem_wait_ld();
-  tmem_ld32(tmem_s_row + 64, ra);
-  fwd_softmax_chunk<kMask>(rb, tmem_p_row + 16, scale_log2, m, i, kv0 + 32, window, len, mx, rowsum);
-  tmem_wait_ld();
-  tmem_ld32(tmem_s_row + 96, rb);
-  fwd_softmax_chunk<kMask>(ra, tmem_p_row + 32, scale_log2, m, i, kv0 + 64, window, len, mx, rowsum);
-  tmem_wait_ld();
-  fwd_softmax_chunk<kMask>(rb, tmem_p_row + 48, scale_log2, m, i, kv0 + 96, window, len, mx, rowsum);
-}
+__device__ __forceinline__ void setmaxnreg_inc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
+__device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -169,6 +171,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   tc_fence_after_sync();
   const uint32_t tmem = sm->tmem_base;
 
+  if (warp >= 8) {
+  setmaxnreg_dec_56();
+
   if (warp == 9) {
     // ------------------------------------ TMA loader ------------------------------------
     if (lane == 0) {
@@ -211,19 +216,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(smem_u32(&sm->bar_s_full[x]));
         }
       }
-      for (int t = 0; ok && t < nt; ++t) {
-        const int s = t % kFwdStages;
-        const int sn = (t + 1) % kFwdStages;
-        if (t + 1 < nt && !(ok = mbar_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1, abort_flag))) break;
-        const uint64_t kn_desc = desc_kmajor(smem_u32(sm->k[sn]));
-        const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
-        for (int x = 0; ok && x < n_act; ++x) {
-          if (!(ok = mbar_wait(smem_u32(&sm->bar_p_full[x]), t & 1, abort_flag))) break;
+      // Serve whichever tile has its P ready first, so that the two softmax warpgroups fall into
+      // anti-phase (one computes while the tensor core works for the other) instead of lockstep.
+      int next_t[2] = {0, n_act == 2 ? 0 : nt};   // next key tile whose P V is to be issued, per tile
+      long long t_idle0 = 0;
+      uint32_t idle = 0;
+      while (ok && (next_t[0] < nt || next_t[1] < nt)) {
+        bool progressed = false;
+#pragma unroll
+        for (int x = 0; x < 2; ++x) {
+          const int t = next_t[x];
+          if (t >= nt) continue;
+          if (!mbar_try_wait(smem_u32(&sm->bar_p_full[x]), t & 1)) continue;
+          if (t >= 1 && !mbar_try_wait(smem_u32(&sm->bar_o_empty[x]), (t - 1) & 1)) continue;
+          const int sn = (t + 1) % kFwdStages;
+          if (t + 1 < nt && !mbar_try_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1)) continue;
           tc_fence_after_sync();
-          if (t >= 1) {
-            if (!(ok = mbar_wait(smem_u32(&sm->bar_o_empty[x]), (t - 1) & 1, abort_flag))) break;
-            tc_fence_after_sync();
-          }
+          const int s = t % kFwdStages;
+          const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
             umma_ts(tmem + 384 + x * 64, tmem + 256 + x * 64 + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, kk > 0);
@@ -231,18 +241,34 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // S of the next key tile goes behind P V in the pipe: when it is ready, P has been read
           // and the softmax threads may overwrite the P columns.
           if (t + 1 < nt) {
+            const uint64_t kn_desc = desc_kmajor(smem_u32(sm->k[sn]));
 #pragma unroll
             for (int kk = 0; kk < kHeadDim / 16; ++kk)
               umma_ss(tmem + x * 128, q_desc[x] + kk * kDescKStepKMajor, kn_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
             umma_commit(smem_u32(&sm->bar_s_full[x]));
           }
+          next_t[x] = t + 1;
+          // K[s], V[s] are free once both tiles' MMAs on them retire
+          if (next_t[x ^ 1] > t) umma_commit(smem_u32(&sm->bar_kv_empty[s]));
+          progressed = true;
         }
-        if (ok) umma_commit(smem_u32(&sm->bar_kv_empty[s]));  // K[s], V[s] are free once these MMAs retire
+        if (progressed) {
+          idle = 0;
+        } else if ((++idle & 1023u) == 0u) {   // bounded: give up after ~2 s without progress
+          if (idle == 1024u) t_idle0 = clock64();
+          if (*abort_flag || clock64() - t_idle0 > kWaitLimitCycles) {
+            sm->abort_flag = 1;
+            ok = false;
+          }
+        }
       }
       if (!ok) report_abort(a);
     }
     __syncwarp();
-  } else if (warp < 4 * n_act) {
+  }
+  } else {
+  setmaxnreg_inc_224();
+  if (warp < 4 * n_act) {
     // -------------------------------------- softmax --------------------------------------
     const int x = warp >> 2;                                      // tile A or B
     const int h = h0 + x;
@@ -276,21 +302,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         mbar_arrive(bar_oe);
       }
       tc_fence_after_sync();
-      float mx = -INFINITY, rowsum = 0.f;
-      if (need_mask) fwd_softmax_pass<true>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
-      else fwd_softmax_pass<false>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
-      alpha = 1.f;
-      if (__any_sync(0xffffffffu, mx > kRescaleThreshold)) {
-        // some row outgrew the reference maximum: move it up and redo this tile
-        const float m_new = m + fmaxf(mx, 0.f);
-        alpha = fast_exp2(m - m_new);
-        m = m_new;
-        mx = -INFINITY;
-        rowsum = 0.f;
-        tmem_wait_st();
-        if (need_mask) fwd_softmax_pass<true>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
-        else fwd_softmax_pass<false>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, mx, rowsum);
-      }
+      float rowsum;
+      const float m_new = need_mask
+          ? fwd_softmax_row<true>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, rowsum)
+          : fwd_softmax_row<false>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, rowsum);
+      alpha = fast_exp2(m - m_new);
+      m = m_new;
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar_p);
@@ -311,6 +328,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       a.lse[((long long)(b * a.Hq + h)) * a.S_pad + i] = (i < len) ? (m + log2f(z)) * kLn2 : 0.f;
     }
+  }
   }
 
   tc_fence_before_sync();

@@ -2,8 +2,8 @@
 // mbarrier, TMA (cp.async.bulk[.tensor]), tensor memory (tcgen05.alloc/ld/st) and the
 // 5th-generation tensor core (tcgen05.mma / tcgen05.commit).
 //
-// Every wait in this file is bounded: it gives up after kWaitLimitNs of wall time or as
-// soon as another thread of the CTA has raised the CTA-wide abort flag, and reports that
+// Every wait in this file is bounded: it gives up after kWaitLimitCycles SM cycles (~2 s) or
+// as soon as another thread of the CTA has raised the CTA-wide abort flag, and reports that
 // to its caller instead of spinning forever.
 #pragma once
 #include <cuda_bf16.h>
@@ -52,18 +52,24 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
-constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s: far beyond any legitimate wait
+constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s of SM clock: far beyond any legitimate wait
 
 // Bounded wait for the phase with the given parity to complete.  Returns false when the
-// wait was abandoned; *abort_flag (a word in shared memory) is then non-zero.
+// wait was abandoned; *abort_flag (a word in shared memory) is then non-zero.  The bound is
+// kept off the fast path: the first polls read no clock at all (reading %globaltimer costs
+// on the order of a microsecond, which on a per-tile dependency chain is the whole budget),
+// later ones look at the SM cycle counter and the abort flag once every 256 polls.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+#pragma unroll 1
+  for (int it = 0; it < 256; ++it)
+    if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+#pragma unroll 1
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((it & 63u) == 0u) {
+    if ((it & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      if (clock64() - t0 > kWaitLimitCycles) {
         *abort_flag = 1;
         return false;
       }
@@ -73,9 +79,10 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
 
 // Short bounded wait used while abandoning a CTA: lets copies that are still in flight land.
 __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
-  const uint64_t t0 = global_timer_ns();
+  const long long t0 = clock64();
+#pragma unroll 1
   for (uint32_t it = 1; !mbar_try_wait(bar, parity); ++it)
-    if ((it & 63u) == 0u && global_timer_ns() - t0 > 50000000ull) return;  // 50 ms
+    if ((it & 63u) == 0u && clock64() - t0 > 100000000ll) return;  // ~50 ms
 }
 
 // Make the outcome of a bounded wait uniform across the warp, so that a whole warp either
