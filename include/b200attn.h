@@ -79,7 +79,7 @@ typedef struct b200attn_params {
   /* backward only */
   b200attn_tensor d_o;        /* gradient of o */
   b200attn_tensor dq, dk, dv; /* outputs, fully overwritten (no pre-zeroing needed) */
-  float* delta;               /* (B,Hq,S_pad) fp32 scratch: rowsum(dO*O) */
+  float* delta;               /* (2,B,Hq,S_pad) fp32 scratch: [0] rowsum(dO*O), [1] -lse*log2(e) */
   float* dsinks;              /* (Hq) fp32 output, overwritten */
   float* dsinks_partial;      /* fp32 scratch of b200attn_dsinks_scratch_floats() elements */
 } b200attn_params;
@@ -116,8 +116,8 @@ int b200attn_bwd(const b200attn_params* p);
 
 /* Backward stages, exported separately so that each can be timed and tested alone. */
 
-/* delta = rowsum(dO * O).  Replaces `_attn_bwd_precompute_D` (attention_kernel.py:102-120).
- * Reads o, dO; writes delta. */
+/* delta[0] = rowsum(dO * O), delta[1] = -lse * log2(e).  Replaces `_attn_bwd_precompute_D`
+ * (attention_kernel.py:102-120).  Reads o, dO, lse; writes delta. */
 int b200attn_bwd_preprocess(const b200attn_params* p);
 
 /* dsinks[h] = sum of the per-warp partials the dq stage wrote (fixed order, warp-shuffle tree:

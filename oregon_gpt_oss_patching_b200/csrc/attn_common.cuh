@@ -39,6 +39,7 @@ struct KernelArgs {
   float* dsinks;                    // (Hq)
   float* dsinks_partial;            // (Hq, B * S_pad/128)
   StridedPtr o, d_o, dq, dk, dv;    // tensors touched with plain loads/stores
+  StridedPtr q, k, v;
 };
 
 __device__ __forceinline__ int seq_len(const KernelArgs& a, int b) {

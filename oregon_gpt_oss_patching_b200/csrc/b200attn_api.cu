@@ -134,6 +134,7 @@ KernelArgs make_args(const b200attn_params* p) {
   a.dsinks = p->dsinks;
   a.dsinks_partial = p->dsinks_partial;
   a.o = strided(p->o); a.d_o = strided(p->d_o); a.dq = strided(p->dq); a.dk = strided(p->dk); a.dv = strided(p->dv);
+  a.q = strided(p->q); a.k = strided(p->k); a.v = strided(p->v);
   return a;
 }
 
@@ -172,7 +173,7 @@ int64_t b200attn_padded_len(int64_t S) { return (S + B200ATTN_ROW_TILE - 1) / B2
 
 int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p) {
   if (p == nullptr) return 0;
-  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 4;
+  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 8;
 }
 
 int b200attn_fwd(const b200attn_params* p) {
@@ -219,16 +220,14 @@ int b200attn_bwd_dkdv(const b200attn_params* p) {
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
-  CUtensorMap tq, tk, tv, tdo;
-  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
-  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
-  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
-  if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
+  CUtensorMap tq, tdo;
+  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kBlk))) return rc;
+  if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kBlk))) return rc;
   const KernelArgs a = make_args(p);
   const size_t smem = sizeof(DkvSmem) + 1024;
   if ((rc = set_smem(attn_bwd_dkdv_kernel, smem))) return rc;
   dim3 grid(a.S_pad / kTile, p->Hkv, p->B);
-  attn_bwd_dkdv_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+  attn_bwd_dkdv_kernel<<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tdo, a);
   return launch_status();
 }
 
@@ -237,16 +236,14 @@ int b200attn_bwd_dq(const b200attn_params* p) {
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
-  CUtensorMap tq, tk, tv, tdo;
-  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
-  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
-  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
-  if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
+  CUtensorMap tk, tv;
+  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kBlk))) return rc;
+  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kBlk))) return rc;
   const KernelArgs a = make_args(p);
   const size_t smem = sizeof(DqSmem) + 1024;
   if ((rc = set_smem(attn_bwd_dq_kernel, smem))) return rc;
   dim3 grid(a.S_pad / kTile, p->Hq, p->B);
-  attn_bwd_dq_kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+  attn_bwd_dq_kernel<<<grid, kDqThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tk, tv, a);
   return launch_status();
 }
 

@@ -1,12 +1,13 @@
 // dQ kernel for sm_100a.
 //
-// One CTA = one 128-row query tile of one query head of one sequence; it loops over the
-// key tiles that tile can see.  Per key tile, on tcgen05 with accumulators in tensor memory:
-//     S  = Q K^T          dP = dO V^T
+// One CTA = one 128-row query tile of one query head of one sequence; it streams the 64-key
+// blocks that tile can see.  Per step (one key block), on tcgen05 with accumulators in tensor
+// memory:
+//     S  = Q K^T          dP = dO V^T                          (N = 64)
 // then with one thread per query row
 //     P  = 2^(S*scale*log2e - LSE*log2e)      dS = P * (dP - delta)
 // dS goes back to tensor memory as bf16 and is the A operand of
-//     dQ += dS K          (accumulated in tensor memory over all key tiles)
+//     dQ += dS K          (accumulated in tensor memory over all key blocks)
 // and the epilogue stores dQ * scale.  This is the dq part of the reference's `_attn_bwd`
 // (attention_kernel.py:190-199, :206-207, :214-217).
 //
@@ -16,31 +17,74 @@
 // stored O that delta = rowsum(dO*O) carries -- and the CTA writes, per warp,
 //     - sum_i exp(sink - LSE_i) * (sum_j P_ij dP_ij)
 // to the dSinks scratch (the reference's per-tile term, attention_kernel.py:173-175).
+//
+// Q and dO (the A operands of S and dP for the CTA's whole life) are copied once into tensor
+// memory as bf16, so those MMAs read only the 64-row K/V block from shared memory.  Pipeline
+// as in the dK/dV kernel: warp 9 streams K/V blocks through a 4-stage TMA ring, warp 8 issues
+// every MMA from a first-ready service loop, S/dP rotate through three tensor-memory buffers,
+// two compute warpgroups take the steps alternately.  Every wait is bounded.
 #pragma once
 #include "attn_common.cuh"
+#include "bwd_dkdv_kernel.cuh"  // kBlk, kBlkBytes
 
 namespace b200attn {
 
-constexpr int kDqStages = 2;
-constexpr int kDqTmemCols = 512;  // S / dS: [0,128)   dP: [128,256)   dQ: [256,320)
+constexpr int kDqStages = 4;
+constexpr int kDqBufs = 3;
+constexpr int kDqThreads = 384;
+constexpr int kDqTmemCols = 512;
+// tensor-memory columns: buffer b: S/dS [128b, 128b+64)  dP [128b+64, 128b+128);
+// Q bf16 [384,416)  dO bf16 [416,448)  dQ [448,512)
 
 struct DqSmem {
-  alignas(1024) uint8_t q[kTileBytes];
-  alignas(1024) uint8_t d_o[kTileBytes];
-  alignas(1024) uint8_t k[kDqStages][kTileBytes];
-  alignas(1024) uint8_t v[kDqStages][kTileBytes];
-  alignas(8) uint64_t bar_q;   // Q and dO landed
-  uint64_t bar_kv[kDqStages];  // K and V of a stage landed
-  uint64_t bar_s;              // S and dP ready
-  uint64_t bar_p;              // dS written by 128 threads
-  uint64_t bar_o;              // dQ MMA of a tile finished (stage + S/dP columns reusable)
+  alignas(1024) uint8_t k[kDqStages][kBlkBytes];
+  alignas(1024) uint8_t v[kDqStages][kBlkBytes];
+  alignas(8) uint64_t bar_q;               // Q and dO copied into tensor memory (256 arrivals)
+  uint64_t bar_in_full[kDqStages];         // K and V block of a stage landed
+  uint64_t bar_in_empty[kDqStages];        // the MMAs reading a stage retired
+  uint64_t bar_s_full[kDqBufs];            // S and dP of a buffer ready
+  uint64_t bar_p_full[kDqBufs];            // dS written (128 arrivals)
+  uint64_t bar_acc;                        // every MMA retired: dQ final
   uint32_t tmem_base;
   int abort_flag;
+  int loads_issued;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
-attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-                   const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+// One step for one query row: reads the 64 S and dP values of the row, writes dS (bf16) back
+// over consumed S columns, adds sum_j P*dP to pdp.
+template <bool kMask>
+__device__ __forceinline__ void dq_compute_step(uint32_t buf, float scale_log2, float nl2, float delta, int i, int kv0,
+                                                int window, int len, float& pdp) {
+  uint32_t rs[2][32], rp[2][32];
+  tmem_ld32(buf, rs[0]);
+  tmem_ld32(buf + 64, rp[0]);
+  tmem_ld32(buf + 32, rs[1]);
+  tmem_ld32(buf + 96, rp[1]);
+  tmem_wait_ld();
+  float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+  for (int c = 0; c < 2; ++c) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float p0 = fast_exp2(fmaf(__uint_as_float(rs[c][e]), scale_log2, nl2));
+      float p1 = fast_exp2(fmaf(__uint_as_float(rs[c][e + 1]), scale_log2, nl2));
+      if (kMask) {
+        if (!visible(i, kv0 + c * 32 + e, window, len)) p0 = 0.f;
+        if (!visible(i, kv0 + c * 32 + e + 1, window, len)) p1 = 0.f;
+      }
+      const float dp0 = __uint_as_float(rp[c][e]), dp1 = __uint_as_float(rp[c][e + 1]);
+      acc0 = fmaf(p0, dp0, acc0);
+      acc1 = fmaf(p1, dp1, acc1);
+      pk[e >> 1] = pack_bf16(p0 * (dp0 - delta), p1 * (dp1 - delta));
+    }
+    tmem_st16(buf + c * 16, pk);  // dS over consumed S columns
+  }
+  pdp += acc0 + acc1;
+}
+
+__global__ void __launch_bounds__(kDqThreads, 1)
+attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                    const KernelArgs a) {
   extern __shared__ uint8_t smem_raw[];
   DqSmem* sm = reinterpret_cast<DqSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -51,36 +95,43 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   const int b = blockIdx.z;
   const int h = blockIdx.y;
   const int g = h / a.group;
-  const int qt = gridDim.x - 1 - blockIdx.x;
+  const int qt = gridDim.x - 1 - blockIdx.x;  // long (late) tiles first
   const int q0 = qt * kTile;
   const int len = seq_len(a, b);
 
-  float* ds_partial = a.dsinks_partial + (((long long)h * a.B + b) * (a.S_pad / kTile) + qt) * 4;
+  // eight per-warp sink-gradient partials per query tile
+  float* ds_partial = a.dsinks_partial + (((long long)h * a.B + b) * (a.S_pad / kTile) + qt) * 8;
   if (q0 >= len) {  // padding only: dQ rows are zero, no sink gradient
     if (tid < kComputeThreads && q0 + tid < a.S) zero_row(a.dq.row(b, h, q0 + tid));
-    if (tid < 4) ds_partial[tid] = 0.f;
+    if (tid < 8) ds_partial[tid] = 0.f;
     return;
   }
 
-  const int hi = min(q0 + kTile - 1, len - 1);
-  const int lo = a.window ? max(0, q0 - a.window + 1) : 0;
-  const int t_first = lo / kTile;
-  const int nt = hi / kTile - t_first + 1;
+  const int hi = min(q0 + kTile - 1, len - 1);              // last visible key
+  const int lo = a.window ? max(0, q0 - a.window + 1) : 0;  // first visible key
+  const int kb_first = lo / kBlk;
+  const int n_steps = hi / kBlk - kb_first + 1;
+  const float* nlse_base = a.delta + (long long)a.B * a.Hq * a.S_pad;  // second half of the delta scratch
 
-  const uint32_t bar_q = smem_u32(&sm->bar_q), bar_s = smem_u32(&sm->bar_s), bar_p = smem_u32(&sm->bar_p),
-                 bar_o = smem_u32(&sm->bar_o);
+  const uint32_t bar_q = smem_u32(&sm->bar_q), bar_acc = smem_u32(&sm->bar_acc);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
-    mbar_init(bar_q, 1);
-    for (int s = 0; s < kDqStages; ++s) mbar_init(smem_u32(&sm->bar_kv[s]), 1);
-    mbar_init(bar_s, 1);
-    mbar_init(bar_p, kComputeThreads);
-    mbar_init(bar_o, 1);
+    mbar_init(bar_q, 2 * kComputeThreads);
+    for (int s = 0; s < kDqStages; ++s) {
+      mbar_init(smem_u32(&sm->bar_in_full[s]), 1);
+      mbar_init(smem_u32(&sm->bar_in_empty[s]), 1);
+    }
+    for (int s = 0; s < kDqBufs; ++s) {
+      mbar_init(smem_u32(&sm->bar_s_full[s]), 1);
+      mbar_init(smem_u32(&sm->bar_p_full[s]), kComputeThreads);
+    }
+    mbar_init(bar_acc, 1);
     sm->abort_flag = 0;
+    sm->loads_issued = 0;
     fence_mbar_init();
   }
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
     tmem_alloc(smem_u32(&sm->tmem_base), kDqTmemCols);
     tmem_relinquish();
@@ -89,126 +140,142 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_dq = tmem + 256;
+  const uint32_t tmem_q = tmem + 384, tmem_do = tmem + 416, tmem_dq = tmem + 448;
 
-  if (warp == 4) {
+  if (warp == 9) {
+    // ------------------------------------ TMA loader ------------------------------------
     if (lane == 0) {
-      prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
-      prefetch_tmap(&tm_do);
-      mbar_arrive_expect_tx(bar_q, 2 * kTileBytes);
-      tma_load_4d(smem_u32(sm->q), &tm_q, bar_q, 0, q0, h, b);
-      tma_load_4d(smem_u32(sm->d_o), &tm_do, bar_q, 0, q0, h, b);
-      const int pre = nt < kDqStages ? nt : kDqStages;
-      for (int s = 0; s < pre; ++s) {
-        const int kv0 = (t_first + s) * kTile;
-        mbar_arrive_expect_tx(smem_u32(&sm->bar_kv[s]), 2 * kTileBytes);
-        tma_load_4d(smem_u32(sm->k[s]), &tm_k, smem_u32(&sm->bar_kv[s]), 0, kv0, g, b);
-        tma_load_4d(smem_u32(sm->v[s]), &tm_v, smem_u32(&sm->bar_kv[s]), 0, kv0, g, b);
-      }
-      const uint32_t idesc_nt = make_idesc_bf16(kTile, kTile, 0, 0);      // A, B both K-contiguous
-      const uint32_t idesc_dq = make_idesc_bf16(kTile, kHeadDim, 0, 1);   // A in TMEM, B = K read N-contiguous
-      const uint64_t q_desc = desc_kmajor(smem_u32(sm->q));
-      const uint64_t do_desc = desc_kmajor(smem_u32(sm->d_o));
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
-      int issued = pre, waited = 0;
-      for (int t = 0; ok && t < nt; ++t) {
-        const int s = t % kDqStages;
-        const uint32_t ph = (t / kDqStages) & 1;
-        if (!(ok = mbar_wait(smem_u32(&sm->bar_kv[s]), ph, abort_flag))) break;
-        waited = t + 1;
-        tc_fence_after_sync();
-        const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
-        const uint64_t v_desc = desc_kmajor(smem_u32(sm->v[s]));
-#pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_nt, kk > 0);
-#pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          umma_ss(tmem_dp, do_desc + kk * kDescKStepKMajor, v_desc + kk * kDescKStepKMajor, idesc_nt, kk > 0);
-        umma_commit(bar_s);
-        if (!(ok = mbar_wait(bar_p, t & 1, abort_flag))) break;
-        tc_fence_after_sync();
-        const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem_dq, tmem_s + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_dq, (t > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar_o);
-        if (t + kDqStages < nt) {
-          if (!(ok = mbar_wait(bar_o, t & 1, abort_flag))) break;
-          const int kv0 = (t_first + t + kDqStages) * kTile;
-          mbar_arrive_expect_tx(smem_u32(&sm->bar_kv[s]), 2 * kTileBytes);
-          tma_load_4d(smem_u32(sm->k[s]), &tm_k, smem_u32(&sm->bar_kv[s]), 0, kv0, g, b);
-          tma_load_4d(smem_u32(sm->v[s]), &tm_v, smem_u32(&sm->bar_kv[s]), 0, kv0, g, b);
-          ++issued;
+      for (int it = 0; it < n_steps; ++it) {
+        const int s = it % kDqStages;
+        if (it >= kDqStages && !mbar_wait(smem_u32(&sm->bar_in_empty[s]), ((it / kDqStages) - 1) & 1, abort_flag)) {
+          report_abort(a);
+          break;
         }
-      }
-      if (!ok) {
-        report_abort(a);
-        mbar_wait_drain(bar_q, 0);
-        for (int t = waited; t < issued; ++t)
-          mbar_wait_drain(smem_u32(&sm->bar_kv[t % kDqStages]), (t / kDqStages) & 1);
+        const int kv0 = (kb_first + it) * kBlk;
+        const uint32_t bar = smem_u32(&sm->bar_in_full[s]);
+        mbar_arrive_expect_tx(bar, 2 * kBlkBytes);
+        tma_load_4d(smem_u32(sm->k[s]), &tm_k, bar, 0, kv0, g, b);
+        tma_load_4d(smem_u32(sm->v[s]), &tm_v, bar, 0, kv0, g, b);
+        *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
       }
     }
     __syncwarp();
-  } else {
-    const int i = q0 + tid;
-    const uint32_t lane_addr = uint32_t(warp * 32) << 16;
-    const long long row_off = ((long long)(b * a.Hq + h)) * a.S_pad + i;
-    const float neg_lse2 = -a.lse[row_off] * kLog2e;
-    const float delta = a.delta[row_off];
-    float pdp = 0.f;  // sum_j P_ij dP_ij in fp32
-    bool ok = true;
-    uint32_t rs[32], rp[32];
-
-    for (int t = 0; t < nt; ++t) {
-      const int kv0 = (t_first + t) * kTile;
-      const bool need_mask = tile_needs_mask(q0, kv0, a.window, len);
-      if (!(ok = warp_all(mbar_wait(bar_s, t & 1, abort_flag)))) break;
+  } else if (warp == 8) {
+    // ------------------------------------ MMA issuer ------------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_front = make_idesc_bf16(kTile, kBlk, 0, 0);     // A in TMEM, B K-contiguous, N = 64
+      const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
+      bool ok = mbar_wait(bar_q, 0, abort_flag);
       tc_fence_after_sync();
+      int front = 0, back = 0;  // next step whose S/dP resp. dQ MMAs are to be issued
+      long long t_idle0 = 0;
+      uint32_t idle = 0;
+      while (ok && back < n_steps) {
+        bool progressed = false;
+        if (back < front && mbar_try_wait(smem_u32(&sm->bar_p_full[back % kDqBufs]), (back / kDqBufs) & 1)) {
+          tc_fence_after_sync();
+          const int s = back % kDqStages;
+          const uint32_t buf = tmem + (back % kDqBufs) * 128;
+          const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        tmem_ld32(tmem_s + lane_addr + c * 32, rs);
-        tmem_ld32(tmem_dp + lane_addr + c * 32, rp);
-        tmem_wait_ld();
-        uint32_t pk[16];
-#pragma unroll
-        for (int e = 0; e < 32; e += 2) {
-          float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), a.scale_log2, neg_lse2));
-          float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), a.scale_log2, neg_lse2));
-          if (need_mask) {
-            if (!visible(i, kv0 + c * 32 + e, a.window, len)) p0 = 0.f;
-            if (!visible(i, kv0 + c * 32 + e + 1, a.window, len)) p1 = 0.f;
-          }
-          pdp = fmaf(p0, __uint_as_float(rp[e]), pdp);
-          pdp = fmaf(p1, __uint_as_float(rp[e + 1]), pdp);
-          const float ds0 = p0 * (__uint_as_float(rp[e]) - delta);
-          const float ds1 = p1 * (__uint_as_float(rp[e + 1]) - delta);
-          pk[e >> 1] = pack_bf16(ds0, ds1);
+          for (int kk = 0; kk < kBlk / 16; ++kk)
+            umma_ts(tmem_dq, buf + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, (back > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(smem_u32(&sm->bar_in_empty[s]));  // the stage (and the buffer) are free once these retire
+          if (back == n_steps - 1) umma_commit(bar_acc);
+          ++back;
+          progressed = true;
         }
-        // dS chunk c overwrites columns [16c, 16c+16) of S, which this thread has consumed
-        tmem_st16(tmem_s + lane_addr + c * 16, pk);
+        if (front < n_steps && front < back + kDqBufs &&
+            mbar_try_wait(smem_u32(&sm->bar_in_full[front % kDqStages]), (front / kDqStages) & 1)) {
+          tc_fence_after_sync();
+          const int s = front % kDqStages;
+          const uint32_t buf = tmem + (front % kDqBufs) * 128;
+          const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
+          const uint64_t v_desc = desc_kmajor(smem_u32(sm->v[s]));
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)
+            umma_ts(buf, tmem_q + kk * 8, k_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)
+            umma_ts(buf + 64, tmem_do + kk * 8, v_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+          umma_commit(smem_u32(&sm->bar_s_full[front % kDqBufs]));
+          ++front;
+          progressed = true;
+        }
+        if (progressed) {
+          idle = 0;
+        } else if ((++idle & 1023u) == 0u) {  // bounded: give up after ~2 s without progress
+          if (idle == 1024u) t_idle0 = clock64();
+          if (*abort_flag || clock64() - t_idle0 > kWaitLimitCycles) {
+            sm->abort_flag = 1;
+            ok = false;
+          }
+        }
       }
+      if (!ok) report_abort(a);
+    }
+    __syncwarp();
+  } else if (warp < 8) {
+    // ------------------------------------- compute --------------------------------------
+    const int wg = warp >> 2;             // takes steps wg, wg+2, ...
+    const int r = tid & 127;
+    const int i = q0 + r;                 // this thread's query position
+    const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
+    const long long row_off = ((long long)(b * a.Hq + h)) * a.S_pad + i;
+    const float nl2 = nlse_base[row_off];  // -LSE * log2(e)
+    const float delta = a.delta[row_off];
+    float pdp = 0.f;                       // this warpgroup's share of sum_j P_ij dP_ij
+    bool ok = true;
+
+    {  // copy this thread's row of Q (warpgroup 0) or dO (warpgroup 1) into tensor memory as bf16
+      uint32_t w[32];
+      if (i < a.S) {
+        const uint4* row = reinterpret_cast<const uint4*>(wg == 0 ? a.q.row(b, h, i) : a.d_o.row(b, h, i));
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const uint4 x = row[c];
+          w[4 * c] = x.x; w[4 * c + 1] = x.y; w[4 * c + 2] = x.z; w[4 * c + 3] = x.w;
+        }
+      } else {
+#pragma unroll
+        for (int c = 0; c < 32; ++c) w[c] = 0u;
+      }
+      tmem_st32((wg == 0 ? tmem_q : tmem_do) + lane_addr, w);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar_p);
+      mbar_arrive(bar_q);
     }
 
-    if (ok) ok = warp_all(mbar_wait(bar_o, (nt - 1) & 1, abort_flag));
+    for (int it = wg; it < n_steps; it += 2) {
+      const int bi = it % kDqBufs;
+      const int kv0 = (kb_first + it) * kBlk;
+      const bool need_mask = (kv0 + kBlk - 1 > q0) || (a.window != 0 && kv0 <= q0 + kTile - 1 - a.window) || (q0 + kTile > len);
+      if (!(ok = warp_all(mbar_wait(smem_u32(&sm->bar_s_full[bi]), (it / kDqBufs) & 1, abort_flag)))) break;
+      tc_fence_after_sync();
+      const uint32_t buf = tmem + bi * 128 + lane_addr;
+      if (need_mask) dq_compute_step<true>(buf, a.scale_log2, nl2, delta, i, kv0, a.window, len, pdp);
+      else dq_compute_step<false>(buf, a.scale_log2, nl2, delta, i, kv0, a.window, len, pdp);
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sm->bar_p_full[bi]));
+    }
+
+    if (ok) ok = warp_all(mbar_wait(bar_acc, 0, abort_flag));
     if (ok) {
-      // sink gradient of this warp's 32 rows (fixed-order shuffle tree)
-      float dsk = (i < len) ? -fast_exp2(fmaf(a.sinks[h], kLog2e, neg_lse2)) * pdp : 0.f;
+      // sink gradient of this warp's 32 rows for this warpgroup's key blocks (fixed-order shuffle tree)
+      float dsk = (i < len) ? -fast_exp2(fmaf(a.sinks[h], kLog2e, nl2)) * pdp : 0.f;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) dsk += __shfl_xor_sync(0xffffffffu, dsk, off);
       if (lane == 0) ds_partial[warp] = dsk;
+      // warpgroup 0 stores dQ columns 0-31, warpgroup 1 columns 32-63
       tc_fence_after_sync();
-      uint32_t r0[32], r1[32];
-      tmem_ld32(tmem_dq + lane_addr, r0);
-      tmem_ld32(tmem_dq + lane_addr + 32, r1);
+      uint32_t r0[32];
+      tmem_ld32(tmem_dq + lane_addr + wg * 32, r0);
       tmem_wait_ld();
       if (i < a.S) {
-        __nv_bfloat16* dst = a.dq.row(b, h, i);
+        __nv_bfloat16* dst = a.dq.row(b, h, i) + wg * 32;
         const float sc = (i < len) ? a.scale : 0.f;
 #pragma unroll
         for (int c = 0; c < 32; c += 8)
@@ -216,21 +283,21 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_consta
                        pack_bf16(__uint_as_float(r0[c + 2]) * sc, __uint_as_float(r0[c + 3]) * sc),
                        pack_bf16(__uint_as_float(r0[c + 4]) * sc, __uint_as_float(r0[c + 5]) * sc),
                        pack_bf16(__uint_as_float(r0[c + 6]) * sc, __uint_as_float(r0[c + 7]) * sc));
-#pragma unroll
-        for (int c = 0; c < 32; c += 8)
-          store_bf16x8(dst + 32 + c, pack_bf16(__uint_as_float(r1[c]) * sc, __uint_as_float(r1[c + 1]) * sc),
-                       pack_bf16(__uint_as_float(r1[c + 2]) * sc, __uint_as_float(r1[c + 3]) * sc),
-                       pack_bf16(__uint_as_float(r1[c + 4]) * sc, __uint_as_float(r1[c + 5]) * sc),
-                       pack_bf16(__uint_as_float(r1[c + 6]) * sc, __uint_as_float(r1[c + 7]) * sc));
       }
     }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 4) {
+  if (warp == 8) {
     __syncwarp();
     tmem_dealloc(tmem, kDqTmemCols);
+  }
+  if (sm->abort_flag && tid == 9 * 32) {
+    // abandoned: give copies still in flight a bounded chance to land before shared memory goes away
+    const int issued = sm->loads_issued;
+    for (int it = max(0, issued - kDqStages); it < issued; ++it)
+      mbar_wait_drain(smem_u32(&sm->bar_in_full[it % kDqStages]), (it / kDqStages) & 1);
   }
 }
 

@@ -1,7 +1,8 @@
 // Memory-bound backward helpers.
 //
 // attn_bwd_preprocess_kernel:  delta[b,h,i] = sum_c dO[b,h,i,c] * O[b,h,i,c]  in fp32 (the
-// reference's `_attn_bwd_precompute_D`, attention_kernel.py:102-120).
+// reference's `_attn_bwd_precompute_D`, attention_kernel.py:102-120); the second half of the
+// scratch receives -LSE*log2(e), the exponent offset the dK/dV and dQ kernels add per query row.
 //
 // attn_bwd_dsinks_kernel:  dsinks[h] = sum of head h's per-warp partials written by the dQ
 // kernel, in a fixed order with a warp-shuffle tree, so the result is bit-reproducible (the
@@ -34,6 +35,7 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
   const int sub = lane >> 3;       // row within the step
   const int part = lane & 7;       // 16-byte slice of the row
   const long long row_base = ((long long)(b * a.Hq + h)) * a.S_pad + (long long)tile * kTile;
+  const long long nlse_off = (long long)a.B * a.Hq * a.S_pad;  // second half of the scratch: -LSE*log2(e)
 
   uint4 xo[8], xd[8];
 #pragma unroll
@@ -54,7 +56,10 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
     s += __shfl_xor_sync(0xffffffffu, s, 2);
     s += __shfl_xor_sync(0xffffffffu, s, 4);
     const int r = warp * 32 + step * 4 + sub;
-    if (part == 0) a.delta[row_base + r] = s;  // zero for padding rows
+    if (part == 0) {
+      a.delta[row_base + r] = s;  // zero for padding rows
+      a.delta[nlse_off + row_base + r] = -a.lse[row_base + r] * kLog2e;
+    }
   }
 }
 
@@ -62,7 +67,7 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
 __global__ void __launch_bounds__(256) attn_bwd_dsinks_kernel(const KernelArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x;
-  const int n = a.B * (a.S_pad / kTile) * 4;  // four warp partials per query tile
+  const int n = a.B * (a.S_pad / kTile) * 8;  // eight warp partials per query tile
   const float* src = a.dsinks_partial + (long long)h * n;
   float s = 0.f;
   for (int idx = tid; idx < n; idx += 256) s += src[idx];

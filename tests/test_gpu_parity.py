@@ -53,7 +53,7 @@ def test_lse_and_delta_stage(name):
     o = torch.empty(B, S, Hq, d, dtype=torch.bfloat16, device=DEV)
     S_pad = _cabi.padded_len(S)
     lse = torch.full((B, Hq, S_pad), float("nan"), device=DEV)
-    delta = torch.full((B, Hq, S_pad), float("nan"), device=DEV)
+    delta = torch.full((2, B, Hq, S_pad), float("nan"), device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     p = _cabi.Params()
     p.B, p.Hq, p.Hkv, p.S, p.d, p.window, p.scale, p.device = B, Hq, k.shape[1], S, d, g["window"], g["scale"], 0
@@ -76,8 +76,8 @@ def test_lse_and_delta_stage(name):
     want_delta = (do.float() * o.float()).sum(-1).transpose(1, 2)  # (B,Hq,S)
     for b, L in enumerate(lens):
         assert rel_err(lse[b, :, :L], g["triton_lse"][b, :, :L]) < TOL_LSE
-        assert rel_err(delta[b, :, :L], want_delta[b, :, :L]) < 1e-5
-        assert float(delta[b, :, L:].abs().max() if L < S_pad else 0.0) == 0.0
+        assert rel_err(delta[0, b, :, :L], want_delta[b, :, :L]) < 1e-5
+        assert float(delta[0, b, :, L:].abs().max() if L < S_pad else 0.0) == 0.0
     assert rel_err(dsinks, g["hf_dsinks"]) < TOL_DSINKS
 
 
