@@ -53,6 +53,27 @@ __device__ __forceinline__ bool visible(int i, int j, int window, int len) {
   return (j <= i) && (window == 0 || j > i - window) && (i < len);
 }
 
+// Bit e (0..31) set iff lo <= e <= hi.  Branch-free; any lo/hi is allowed (empty when lo > hi).
+__device__ __forceinline__ uint32_t range_bits(int lo, int hi) {
+  const int hc = min(max(hi, -1), 31), lc = min(max(lo, 0), 32);
+  const uint32_t m_hi = hc < 0 ? 0u : (0xffffffffu >> (31 - hc));
+  const uint32_t m_lo = lc > 31 ? 0u : (0xffffffffu << lc);
+  return m_hi & m_lo;
+}
+// Visibility of the 32 keys j0 .. j0+31 for query i, as a bit mask (bit e <-> key j0+e):
+// j <= i, j > i - window (when window > 0), i < len.
+__device__ __forceinline__ uint32_t visible_keys32(int i, int j0, int window, int len) {
+  const int hi = i < len ? i - j0 : -1;
+  const int lo = window ? i - window + 1 - j0 : 0;
+  return range_bits(lo, hi);
+}
+// Visibility of the 32 queries i0 .. i0+31 for key j (bit e <-> query i0+e):
+// i >= j, i < j + window (when window > 0), i < len.
+__device__ __forceinline__ uint32_t visible_queries32(int j, int i0, int window, int len) {
+  const int last = window ? min(j + window - 1, len - 1) : len - 1;
+  return range_bits(j - i0, last - i0);
+}
+
 // Does a (query tile at q0, key tile at kv0) pair contain any masked (i, j)?
 __device__ __forceinline__ bool tile_needs_mask(int q0, int kv0, int window, int len) {
   return (kv0 + kTile - 1 > q0) || (window != 0 && kv0 <= q0 + kTile - 1 - window) || (q0 + kTile > len);

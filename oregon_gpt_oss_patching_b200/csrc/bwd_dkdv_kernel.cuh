@@ -75,6 +75,7 @@ __device__ __forceinline__ void dkv_compute_step(uint32_t buf, const float* nlse
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     uint32_t pp[16], pd[16];
+    const uint32_t bits = kMask ? visible_queries32(j, q0 + c * 32, window, len) : 0xffffffffu;
 #pragma unroll
     for (int e4 = 0; e4 < 8; ++e4) {
       const float4 L = nl4[c * 8 + e4];
@@ -86,7 +87,7 @@ __device__ __forceinline__ void dkv_compute_step(uint32_t buf, const float* nlse
       for (int u = 0; u < 4; ++u) {
         const int e = e4 * 4 + u;
         p[u] = fast_exp2(fmaf(__uint_as_float(rs[c][e]), scale_log2, lv[u]));
-        if (kMask && !visible(q0 + c * 32 + e, j, window, len)) p[u] = 0.f;
+        if (kMask) p[u] = (bits >> e) & 1u ? p[u] : 0.f;  // select, not a branch
         ds[u] = p[u] * (__uint_as_float(rp[c][e]) - dl[u]);
       }
       pp[e4 * 2] = pack_bf16(p[0], p[1]);

@@ -65,13 +65,14 @@ __device__ __forceinline__ void dq_compute_step(uint32_t buf, float scale_log2, 
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     uint32_t pk[16];
+    const uint32_t bits = kMask ? visible_keys32(i, kv0 + c * 32, window, len) : 0xffffffffu;
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
       float p0 = fast_exp2(fmaf(__uint_as_float(rs[c][e]), scale_log2, nl2));
       float p1 = fast_exp2(fmaf(__uint_as_float(rs[c][e + 1]), scale_log2, nl2));
-      if (kMask) {
-        if (!visible(i, kv0 + c * 32 + e, window, len)) p0 = 0.f;
-        if (!visible(i, kv0 + c * 32 + e + 1, window, len)) p1 = 0.f;
+      if (kMask) {  // selects, not branches
+        p0 = (bits >> e) & 1u ? p0 : 0.f;
+        p1 = (bits >> (e + 1)) & 1u ? p1 : 0.f;
       }
       const float dp0 = __uint_as_float(rp[c][e]), dp1 = __uint_as_float(rp[c][e + 1]);
       acc0 = fmaf(p0, dp0, acc0);

@@ -78,12 +78,13 @@ __device__ __forceinline__ float fwd_softmax_row(uint32_t tmem_s_row, uint32_t t
 #pragma unroll
   for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s_row + c * 32, s[c]);
   tmem_wait_ld();
-  if (kMask) {
+  if (kMask) {  // branch-free: one visibility bit mask per 32 keys, then selects
 #pragma unroll
-    for (int c = 0; c < 4; ++c)
+    for (int c = 0; c < 4; ++c) {
+      const uint32_t bits = visible_keys32(i, kv0 + c * 32, window, len);
 #pragma unroll
-      for (int e = 0; e < 32; ++e)
-        if (!visible(i, kv0 + c * 32 + e, window, len)) s[c][e] = 0xff800000u;  // -inf
+      for (int e = 0; e < 32; ++e) s[c][e] = (bits >> e) & 1u ? s[c][e] : 0xff800000u;  // -inf
+    }
   }
   float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
