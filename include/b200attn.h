@@ -49,8 +49,12 @@ enum {
   B200ATTN_EDEVICE = -5,     /* device is not compute capability 10.x             */
   B200ATTN_ECUDA = -6,       /* a CUDA runtime/driver call failed                 */
   B200ATTN_ETENSORMAP = -7,  /* the driver rejected a TMA tensor map              */
-  B200ATTN_ESCRATCH = -8     /* scratch buffer missing or too small               */
+  B200ATTN_ESCRATCH = -8,    /* scratch buffer missing or too small               */
+  B200ATTN_ETOOLARGE = -9    /* larger than b200attn_bwd_static_scratch can take  */
 };
+
+/* Largest B * Hq * b200attn_padded_len(S) that b200attn_bwd_static_scratch accepts. */
+#define B200ATTN_STATIC_MAX_ROWS (1 << 20)
 
 /* bf16 tensor view (batch, head, position, head_dim); strides in ELEMENTS, head_dim stride 1 */
 typedef struct b200attn_tensor {
@@ -134,6 +138,29 @@ int b200attn_bwd_dkdv(const b200attn_params* p);
  * the sink-gradient partials -sum_i exp(sink - lse_i) * sum_j P_ij dP_ij of its rows
  * (attention_kernel.py:173-175) to dsinks_partial.  Reads q,k,v,dO,lse,delta,sinks. */
 int b200attn_bwd_dq(const b200attn_params* p);
+
+/*
+ * Backward for callers that must not allocate.  This entry point has no counterpart in the
+ * reference.  Some hosts of this library cannot call cudaMalloc at the moment they need a
+ * backward pass: code running inside a memory-pool or arena that has already handed out all
+ * device memory, real-time or signal-like contexts where an allocation's latency (or its
+ * implicit synchronisation) is not acceptable, and bindings from runtimes that own the
+ * allocator and do not let foreign code use it.  For them the two scratch buffers of
+ * b200attn_bwd (`delta` and `dsinks_partial`, which are ignored here and may be NULL) live in
+ * a fixed array inside the library's device image: about 8.3 MB that every GPU loading the
+ * library holds until the process exits.  Inputs and outputs are still the caller's.
+ *
+ *   - Limit: B * Hq * b200attn_padded_len(S) <= B200ATTN_STATIC_MAX_ROWS (e.g. B=1, Hq=64,
+ *     S=16384); anything larger returns B200ATTN_ETOOLARGE without launching.
+ *   - The first call on each device looks up the array's device address (one
+ *     cudaGetSymbolAddress per array, with that device current, under a host mutex); make
+ *     that first call outside any stream capture.  No call allocates or frees memory.
+ *   - All calls on a device share the one array and it keeps the previous call's contents;
+ *     every element that is read is overwritten first by the same call, so nothing needs
+ *     clearing, but two calls whose kernels overlap on the GPU (different streams) race.
+ *     Serialise them on one stream or with events.
+ */
+int b200attn_bwd_static_scratch(const b200attn_params* p);
 
 /*
  * Self-test of the tensor-core building blocks, used by the test-suite: D = A * B^T for one

@@ -5,6 +5,8 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <mutex>
+
 #include "attn_common.cuh"
 #include "bwd_dkdv_kernel.cuh"
 #include "bwd_dq_kernel.cuh"
@@ -165,6 +167,7 @@ const char* b200attn_strerror(int code) {
     case B200ATTN_ECUDA: return "a CUDA runtime or driver call failed";
     case B200ATTN_ETENSORMAP: return "the driver rejected a TMA tensor map";
     case B200ATTN_ESCRATCH: return "scratch buffer missing";
+    case B200ATTN_ETOOLARGE: return "problem exceeds the fixed scratch of b200attn_bwd_static_scratch (B*Hq*S_pad > B200ATTN_STATIC_MAX_ROWS)";
     default: return "unknown b200attn error code";
   }
 }
@@ -254,6 +257,52 @@ int b200attn_bwd(const b200attn_params* p) {
   if ((rc = b200attn_bwd_dkdv(p))) return rc;
   if ((rc = b200attn_bwd_dq(p))) return rc;
   return b200attn_bwd_dsinks(p);
+}
+
+// ---- backward without caller-provided scratch ------------------------------------------------
+// Fixed device-resident scratch for b200attn_bwd_static_scratch.  Every GPU that loads the
+// library holds these ~8.3 MB until the process exits.
+constexpr int64_t kStaticMaxRows = B200ATTN_STATIC_MAX_ROWS;
+static __device__ __align__(256) float g_static_delta[2 * kStaticMaxRows];           // delta | -lse*log2(e)
+static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 16];  // 8 partials per 128 rows
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_static_mutex;
+float* g_static_delta_ptr[kMaxDevices] = {};
+float* g_static_partial_ptr[kMaxDevices] = {};
+
+// The arrays' names are host-side stand-ins, not device addresses: resolve them once per device,
+// with that device current.
+int static_scratch_for(int device, float** delta, float** partial) {
+  if (device < 0 || device >= kMaxDevices) return B200ATTN_EDEVICE;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_delta_ptr[device] == nullptr) {
+    void* d = nullptr;
+    void* s = nullptr;
+    if (cudaGetSymbolAddress(&d, g_static_delta) != cudaSuccess) return B200ATTN_ECUDA;
+    if (cudaGetSymbolAddress(&s, g_static_dsinks_partial) != cudaSuccess) return B200ATTN_ECUDA;
+    g_static_delta_ptr[device] = static_cast<float*>(d);
+    g_static_partial_ptr[device] = static_cast<float*>(s);
+  }
+  *delta = g_static_delta_ptr[device];
+  *partial = g_static_partial_ptr[device];
+  return B200ATTN_OK;
+}
+}  // namespace
+
+int b200attn_bwd_static_scratch(const b200attn_params* p) {
+  if (p == nullptr) return B200ATTN_EINVAL;
+  if (p->B <= 0 || p->Hq <= 0 || p->S <= 0) return B200ATTN_EINVAL;
+  const int64_t rows = (int64_t)p->B * p->Hq * b200attn_padded_len(p->S);
+  if (rows > kStaticMaxRows) return B200ATTN_ETOOLARGE;
+  int rc = check_device(p->device);
+  if (rc) return rc;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  b200attn_params q = *p;
+  if ((rc = static_scratch_for(p->device, &q.delta, &q.dsinks_partial))) return rc;
+  return b200attn_bwd(&q);
 }
 
 int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int32_t* status, int device, void* stream) {
