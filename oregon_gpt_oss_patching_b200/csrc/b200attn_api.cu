@@ -223,14 +223,16 @@ int b200attn_bwd_dkdv(const b200attn_params* p) {
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
-  CUtensorMap tq, tdo;
-  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kBlk))) return rc;
-  if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kBlk))) return rc;
+  CUtensorMap tq, tk, tv, tdo;
+  if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
+  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
   const size_t smem = sizeof(DkvSmem) + 1024;
   if ((rc = set_smem(attn_bwd_dkdv_kernel, smem))) return rc;
   dim3 grid(a.S_pad / kTile, p->Hkv, p->B);
-  attn_bwd_dkdv_kernel<<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tdo, a);
+  attn_bwd_dkdv_kernel<<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
   return launch_status();
 }
 
