@@ -242,8 +242,8 @@ int b200attn_bwd_dq(const b200attn_params* p) {
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
   CUtensorMap tk, tv;
-  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kBlk))) return rc;
-  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kBlk))) return rc;
+  if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
   const size_t smem = sizeof(DqSmem) + 1024;
   if ((rc = set_smem(attn_bwd_dq_kernel, smem))) return rc;

@@ -1,13 +1,13 @@
 // dQ kernel for sm_100a.
 //
-// One CTA = one 128-row query tile of one query head of one sequence; it streams the 64-key
-// blocks that tile can see.  Per step (one key block), on tcgen05 with accumulators in tensor
-// memory:
-//     S  = Q K^T          dP = dO V^T                          (N = 64)
+// One CTA = one 128-row query tile of one query head of one sequence; it streams the 128-key
+// tiles that query tile can see.  Per item (one key tile), on tcgen05 with accumulators in
+// tensor memory:
+//     S  = Q K^T          dP = dO V^T                          (N = 128)
 // then with one thread per query row
 //     P  = 2^(S*scale*log2e - LSE*log2e)      dS = P * (dP - delta)
-// dS goes back to tensor memory as bf16 and is the A operand of
-//     dQ += dS K          (accumulated in tensor memory over all key blocks)
+// dS goes to tensor memory as bf16 and is the A operand of
+//     dQ += dS K          (N = 64, accumulated in tensor memory over all key tiles)
 // and the epilogue stores dQ * scale.  This is the dq part of the reference's `_attn_bwd`
 // (attention_kernel.py:190-199, :206-207, :214-217).
 //
@@ -19,53 +19,48 @@
 // to the dSinks scratch (the reference's per-tile term, attention_kernel.py:173-175).
 //
 // Q and dO (the A operands of S and dP for the CTA's whole life) are copied once into tensor
-// memory as bf16, so those MMAs read only the 64-row K/V block from shared memory.  Pipeline
-// as in the dK/dV kernel: warp 9 streams K/V blocks through a 4-stage TMA ring, warp 8 issues
-// every MMA from a first-ready service loop, S/dP rotate through three tensor-memory buffers,
-// two compute warpgroups take the steps alternately.  Every wait is bounded.
+// memory as bf16, so those MMAs read only the K/V tile from shared memory.  Pipeline as in the
+// dK/dV kernel: warp 9 streams K/V tiles through a 3-stage TMA ring, warp 8 issues every MMA
+// from a first-ready service loop, the two compute warpgroups split the 128 key columns of an
+// item, pull their half of S/dP into registers and release those columns at once (the tensor
+// core computes the next item's S/dP under this item's exponentials), and write dS to its own
+// columns once the previous item's dQ MMAs have left them.  Every wait is bounded.
 #pragma once
 #include "attn_common.cuh"
-#include "bwd_dkdv_kernel.cuh"  // kBlk, kBlkBytes
+#include "bwd_dkdv_kernel.cuh"  // setmaxnreg helpers
 
 namespace b200attn {
 
-constexpr int kDqStages = 4;
-constexpr int kDqBufs = 3;
+constexpr int kDqStages = 3;
 constexpr int kDqThreads = 384;
 constexpr int kDqTmemCols = 512;
-// tensor-memory columns: buffer b: S/dS [128b, 128b+64)  dP [128b+64, 128b+128);
-// Q bf16 [384,416)  dO bf16 [416,448)  dQ [448,512)
+// tensor-memory columns: S [0,128)  dP [128,256)  dS bf16 [256,320)  Q bf16 [320,352)  dO bf16 [352,384)  dQ [384,448)
 
 struct DqSmem {
-  alignas(1024) uint8_t k[kDqStages][kBlkBytes];
-  alignas(1024) uint8_t v[kDqStages][kBlkBytes];
+  alignas(1024) uint8_t k[kDqStages][kTileBytes];
+  alignas(1024) uint8_t v[kDqStages][kTileBytes];
   alignas(8) uint64_t bar_q;               // Q and dO copied into tensor memory (256 arrivals)
-  uint64_t bar_in_full[kDqStages];         // K and V block of a stage landed
-  uint64_t bar_in_empty[kDqStages];        // the MMAs reading a stage retired
-  uint64_t bar_s_full[kDqBufs];            // S and dP of a buffer ready
-  uint64_t bar_p_full[kDqBufs];            // dS written (128 arrivals)
+  uint64_t bar_in_full[kDqStages];         // K and V tile of a stage landed
+  uint64_t bar_in_empty[kDqStages];        // the dQ MMAs reading a stage retired
+  uint64_t bar_s_full;                     // S and dP ready                 (tcgen05.commit)
+  uint64_t bar_s_free;                     // S and dP are in registers      (256 arrivals)
+  uint64_t bar_p_full;                     // dS written                     (256 arrivals)
+  uint64_t bar_p_free;                     // the dQ MMAs have read dS       (tcgen05.commit)
   uint64_t bar_acc;                        // every MMA retired: dQ final
   uint32_t tmem_base;
   int abort_flag;
   int loads_issued;
 };
 
-// One step for one query row: reads the 64 S and dP values of the row, writes dS (bf16) back
-// over consumed S columns, adds sum_j P*dP to pdp.
+// dS (bf16 pairs) of 64 key columns for one query row from S/dP in registers; adds sum_j P*dP to pdp.
 template <bool kMask>
-__device__ __forceinline__ void dq_compute_step(uint32_t buf, float scale_log2, float nl2, float delta, int i, int kv0,
-                                                int window, int len, float& pdp) {
-  uint32_t rs[2][32], rp[2][32];
-  tmem_ld32(buf, rs[0]);
-  tmem_ld32(buf + 64, rp[0]);
-  tmem_ld32(buf + 32, rs[1]);
-  tmem_ld32(buf + 96, rp[1]);
-  tmem_wait_ld();
+__device__ __forceinline__ void dq_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], float scale_log2,
+                                           float nl2, float delta, int i, int j0, int window, int len,
+                                           uint32_t (&pk)[2][16], float& pdp) {
   float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    uint32_t pk[16];
-    const uint32_t bits = kMask ? visible_keys32(i, kv0 + c * 32, window, len) : 0xffffffffu;
+    const uint32_t bits = kMask ? visible_keys32(i, j0 + c * 32, window, len) : 0xffffffffu;
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
       float p0 = fast_exp2(fmaf(__uint_as_float(rs[c][e]), scale_log2, nl2));
@@ -77,9 +72,8 @@ __device__ __forceinline__ void dq_compute_step(uint32_t buf, float scale_log2, 
       const float dp0 = __uint_as_float(rp[c][e]), dp1 = __uint_as_float(rp[c][e + 1]);
       acc0 = fmaf(p0, dp0, acc0);
       acc1 = fmaf(p1, dp1, acc1);
-      pk[e >> 1] = pack_bf16(p0 * (dp0 - delta), p1 * (dp1 - delta));
+      pk[c][e >> 1] = pack_bf16(p0 * (dp0 - delta), p1 * (dp1 - delta));
     }
-    tmem_st16(buf + c * 16, pk);  // dS over consumed S columns
   }
   pdp += acc0 + acc1;
 }
@@ -110,11 +104,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
 
   const int hi = min(q0 + kTile - 1, len - 1);              // last visible key
   const int lo = a.window ? max(0, q0 - a.window + 1) : 0;  // first visible key
-  const int kb_first = lo / kBlk;
-  const int n_steps = hi / kBlk - kb_first + 1;
+  const int kt_first = lo / kTile;
+  const int n_items = hi / kTile - kt_first + 1;
   const float* nlse_base = a.delta + (long long)a.B * a.Hq * a.S_pad;  // second half of the delta scratch
 
-  const uint32_t bar_q = smem_u32(&sm->bar_q), bar_acc = smem_u32(&sm->bar_acc);
+  const uint32_t bar_q = smem_u32(&sm->bar_q), bar_acc = smem_u32(&sm->bar_acc), bar_s_full = smem_u32(&sm->bar_s_full),
+                 bar_s_free = smem_u32(&sm->bar_s_free), bar_p_full = smem_u32(&sm->bar_p_full),
+                 bar_p_free = smem_u32(&sm->bar_p_free);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
@@ -123,10 +119,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       mbar_init(smem_u32(&sm->bar_in_full[s]), 1);
       mbar_init(smem_u32(&sm->bar_in_empty[s]), 1);
     }
-    for (int s = 0; s < kDqBufs; ++s) {
-      mbar_init(smem_u32(&sm->bar_s_full[s]), 1);
-      mbar_init(smem_u32(&sm->bar_p_full[s]), kComputeThreads);
-    }
+    mbar_init(bar_s_full, 1);
+    mbar_init(bar_s_free, 2 * kComputeThreads);
+    mbar_init(bar_p_full, 2 * kComputeThreads);
+    mbar_init(bar_p_free, 1);
     mbar_init(bar_acc, 1);
     sm->abort_flag = 0;
     sm->loads_issued = 0;
@@ -141,22 +137,25 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_q = tmem + 384, tmem_do = tmem + 416, tmem_dq = tmem + 448;
+  const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_ds = tmem + 256, tmem_q = tmem + 320, tmem_do = tmem + 352,
+                 tmem_dq = tmem + 384;
 
+  if (warp >= 8) {
+  setmaxnreg_dec_72();
   if (warp == 9) {
     // ------------------------------------ TMA loader ------------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
-      for (int it = 0; it < n_steps; ++it) {
+      for (int it = 0; it < n_items; ++it) {
         const int s = it % kDqStages;
         if (it >= kDqStages && !mbar_wait(smem_u32(&sm->bar_in_empty[s]), ((it / kDqStages) - 1) & 1, abort_flag)) {
           report_abort(a);
           break;
         }
-        const int kv0 = (kb_first + it) * kBlk;
+        const int kv0 = (kt_first + it) * kTile;
         const uint32_t bar = smem_u32(&sm->bar_in_full[s]);
-        mbar_arrive_expect_tx(bar, 2 * kBlkBytes);
+        mbar_arrive_expect_tx(bar, 2 * kTileBytes);
         tma_load_4d(smem_u32(sm->k[s]), &tm_k, bar, 0, kv0, g, b);
         tma_load_4d(smem_u32(sm->v[s]), &tm_v, bar, 0, kv0, g, b);
         *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
@@ -166,43 +165,44 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   } else if (warp == 8) {
     // ------------------------------------ MMA issuer ------------------------------------
     if (lane == 0) {
-      const uint32_t idesc_front = make_idesc_bf16(kTile, kBlk, 0, 0);     // A in TMEM, B K-contiguous, N = 64
+      const uint32_t idesc_front = make_idesc_bf16(kTile, kTile, 0, 0);    // A in TMEM, B K-contiguous, N = 128
       const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
       bool ok = mbar_wait(bar_q, 0, abort_flag);
       tc_fence_after_sync();
-      int front = 0, back = 0;  // next step whose S/dP resp. dQ MMAs are to be issued
+      int front = 0, back = 0;  // next item whose S/dP resp. dQ MMAs are to be issued
       long long t_idle0 = 0;
       uint32_t idle = 0;
-      while (ok && back < n_steps) {
+      while (ok && back < n_items) {
         bool progressed = false;
-        if (back < front && mbar_try_wait(smem_u32(&sm->bar_p_full[back % kDqBufs]), (back / kDqBufs) & 1)) {
-          tc_fence_after_sync();
-          const int s = back % kDqStages;
-          const uint32_t buf = tmem + (back % kDqBufs) * 128;
-          const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));
-#pragma unroll
-          for (int kk = 0; kk < kBlk / 16; ++kk)
-            umma_ts(tmem_dq, buf + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, (back > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(smem_u32(&sm->bar_in_empty[s]));  // the stage (and the buffer) are free once these retire
-          if (back == n_steps - 1) umma_commit(bar_acc);
-          ++back;
-          progressed = true;
-        }
-        if (front < n_steps && front < back + kDqBufs &&
-            mbar_try_wait(smem_u32(&sm->bar_in_full[front % kDqStages]), (front / kDqStages) & 1)) {
+        // S/dP of item `front`: its stage has landed and the previous item's S/dP are in registers
+        if (front < n_items && mbar_try_wait(smem_u32(&sm->bar_in_full[front % kDqStages]), (front / kDqStages) & 1) &&
+            (front == 0 || mbar_try_wait(bar_s_free, (front - 1) & 1))) {
           tc_fence_after_sync();
           const int s = front % kDqStages;
-          const uint32_t buf = tmem + (front % kDqBufs) * 128;
           const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
           const uint64_t v_desc = desc_kmajor(smem_u32(sm->v[s]));
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ts(buf, tmem_q + kk * 8, k_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+            umma_ts(tmem_s, tmem_q + kk * 8, k_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ts(buf + 64, tmem_do + kk * 8, v_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
-          umma_commit(smem_u32(&sm->bar_s_full[front % kDqBufs]));
+            umma_ts(tmem_dp, tmem_do + kk * 8, v_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+          umma_commit(bar_s_full);
           ++front;
+          progressed = true;
+        }
+        // dQ of item `back`: its dS has been written
+        if (back < front && mbar_try_wait(bar_p_full, back & 1)) {
+          tc_fence_after_sync();
+          const int s = back % kDqStages;
+          const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ts(tmem_dq, tmem_ds + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, (back > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(bar_p_free);                      // dS columns reusable once these retire
+          umma_commit(smem_u32(&sm->bar_in_empty[s]));  // and so is the K/V stage
+          if (back == n_items - 1) umma_commit(bar_acc);
+          ++back;
           progressed = true;
         }
         if (progressed) {
@@ -218,9 +218,12 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       if (!ok) report_abort(a);
     }
     __syncwarp();
-  } else if (warp < 8) {
+  }
+  } else {
+  setmaxnreg_inc_216();
+  {
     // ------------------------------------- compute --------------------------------------
-    const int wg = warp >> 2;             // takes steps wg, wg+2, ...
+    const int wg = warp >> 2;             // which 64 key columns of every item
     const int r = tid & 127;
     const int i = q0 + r;                 // this thread's query position
     const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
@@ -249,23 +252,35 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       mbar_arrive(bar_q);
     }
 
-    for (int it = wg; it < n_steps; it += 2) {
-      const int bi = it % kDqBufs;
-      const int kv0 = (kb_first + it) * kBlk;
-      const bool need_mask = (kv0 + kBlk - 1 > q0) || (a.window != 0 && kv0 <= q0 + kTile - 1 - a.window) || (q0 + kTile > len);
-      if (!(ok = warp_all(mbar_wait(smem_u32(&sm->bar_s_full[bi]), (it / kDqBufs) & 1, abort_flag)))) break;
+    for (int it = 0; it < n_items; ++it) {
+      const int j0 = (kt_first + it) * kTile + wg * 64;  // first key column of this thread
+      const bool need_mask = (j0 + 63 > q0) || (a.window != 0 && j0 <= q0 + kTile - 1 - a.window) || (q0 + kTile > len);
+      if (!(ok = warp_all(mbar_wait(bar_s_full, it & 1, abort_flag)))) break;
       tc_fence_after_sync();
-      const uint32_t buf = tmem + bi * 128 + lane_addr;
-      if (need_mask) dq_compute_step<true>(buf, a.scale_log2, nl2, delta, i, kv0, a.window, len, pdp);
-      else dq_compute_step<false>(buf, a.scale_log2, nl2, delta, i, kv0, a.window, len, pdp);
+      uint32_t rs[2][32], rp[2][32];
+      tmem_ld32(tmem_s + lane_addr + wg * 64, rs[0]);
+      tmem_ld32(tmem_dp + lane_addr + wg * 64, rp[0]);
+      tmem_ld32(tmem_s + lane_addr + wg * 64 + 32, rs[1]);
+      tmem_ld32(tmem_dp + lane_addr + wg * 64 + 32, rp[1]);
+      tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(bar_s_free);  // S/dP columns may be overwritten by the next item
+      uint32_t pk[2][16];
+      if (need_mask) dq_compute<true>(rs, rp, a.scale_log2, nl2, delta, i, j0, a.window, len, pk, pdp);
+      else dq_compute<false>(rs, rp, a.scale_log2, nl2, delta, i, j0, a.window, len, pk, pdp);
+      // the dQ MMAs of the previous item must have left the dS columns
+      if (it > 0 && !(ok = warp_all(mbar_wait(bar_p_free, (it - 1) & 1, abort_flag)))) break;
+      tc_fence_after_sync();
+      tmem_st16(tmem_ds + lane_addr + wg * 32, pk[0]);
+      tmem_st16(tmem_ds + lane_addr + wg * 32 + 16, pk[1]);
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(smem_u32(&sm->bar_p_full[bi]));
+      mbar_arrive(bar_p_full);
     }
 
     if (ok) ok = warp_all(mbar_wait(bar_acc, 0, abort_flag));
     if (ok) {
-      // sink gradient of this warp's 32 rows for this warpgroup's key blocks (fixed-order shuffle tree)
+      // sink gradient of this warp's 32 rows for this warpgroup's key columns (fixed-order shuffle tree)
       float dsk = (i < len) ? -fast_exp2(fmaf(a.sinks[h], kLog2e, nl2)) * pdp : 0.f;
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) dsk += __shfl_xor_sync(0xffffffffu, dsk, off);
@@ -286,6 +301,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
                        pack_bf16(__uint_as_float(r0[c + 6]) * sc, __uint_as_float(r0[c + 7]) * sc));
       }
     }
+  }
   }
 
   tc_fence_before_sync();
