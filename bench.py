@@ -45,56 +45,66 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples the SM clock and the throttle reasons through NVML while the timed region runs.
+
+    A thread polls every 10 ms (nvidia-smi's own loop starts too slowly for sub-second regions);
+    falls back to one nvidia-smi query when NVML cannot be loaded.
+    """
+    REASONS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, gpu_index: int):
         self.gpu_index = gpu_index
-        self.proc = None
-        self.lines = []
-        self.thread = None
+        self.samples, self.reason_bits = [], 0
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._nvml = None
 
     def start(self):
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
-                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            import pynvml
+            pynvml.nvmlInit()
+            visible = os.environ.get("CUDA_VISIBLE_DEVICES")
+            index = int(visible.split(",")[self.gpu_index]) if visible and visible.split(",")[0].isdigit() else self.gpu_index
+            self._handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._handle, pynvml.NVML_CLOCK_SM))
+            self._nvml = pynvml
         except Exception:
-            self.proc = None
+            self._nvml = None
             return
-        self.thread = threading.Thread(target=self._pump, daemon=True)
-        self.thread.start()
+        self._thread = threading.Thread(target=self._poll, daemon=True)
+        self._thread.start()
 
-    def _pump(self):
-        for line in self.proc.stdout:
-            self.lines.append(line.strip())
+    def _poll(self):
+        nv = self._nvml
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._handle, nv.NVML_CLOCK_SM)))
+                self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._handle))
+            except Exception:
+                try:
+                    self.reason_bits |= int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._handle))
+                except Exception:
+                    pass
+            self._stop.wait(0.01)
 
     def stop(self) -> dict:
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
+        if self._nvml is None:
+            return self._smi_once()
+        self._stop.set()
+        self._thread.join(timeout=2)
+        reasons = sorted(name for name, bit in self.REASONS.items() if self.reason_bits & bit)
+        return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+                "samples": len(self.samples), "reasons": reasons, "source": "nvml"}
+
+    def _smi_once(self) -> dict:
         try:
-            self.proc.wait(timeout=5)
+            out = subprocess.run(["nvidia-smi", "--query-gpu=clocks.sm,clocks.max.sm", "--format=csv,noheader,nounits",
+                                  "-i", str(self.gpu_index)], capture_output=True, text=True, timeout=10).stdout
+            sm, mx = (float(x) for x in out.strip().split(","))
+            return {"sm_mhz": sm, "sm_max_mhz": mx, "samples": 1, "reasons": [], "source": "nvidia-smi (after the region)"}
         except Exception:
-            self.proc.kill()
-        sm, mx, reasons = [], [], set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for line in self.lines:
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 9:
-                continue
-            try:
-                sm.append(float(parts[1]))
-                mx.append(float(parts[2]))
-            except ValueError:
-                continue
-            for name, val in zip(names, parts[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+            return {"sm_mhz": None, "sm_max_mhz": None, "samples": 0, "reasons": ["clock query unavailable"]}
 
 
 # --------------------------------------------------------------------------------------------
@@ -153,9 +163,8 @@ def run_b200(args, rank, world, local_rank):
     p = _cabi.Params()
     p.B, p.Hq, p.Hkv, p.S, p.d, p.window, p.scale, p.device = B, Hq, Hkv, S, d, case.window, case.scale, local_rank
     stream = torch.cuda.current_stream(dev)
-    p.stream, p.status, p.sinks = stream.cuda_stream, status.data_ptr(), sinks.float().data_ptr()
-    sinks_f32 = sinks.float()
-    p.sinks = sinks_f32.data_ptr()
+    sinks_f32 = sinks.float().contiguous()
+    p.stream, p.status, p.sinks = stream.cuda_stream, status.data_ptr(), sinks_f32.data_ptr()
     p.seqlens = seqlens.data_ptr() if seqlens is not None else None
     p.q, p.k, p.v = (_cabi.tensor4(t, "bhsd") for t in (qd, kd, vd))
     p.o, p.d_o, p.lse, p.delta = _cabi.tensor4(o, "bshd"), _cabi.tensor4(dod, "bshd"), lse.data_ptr(), delta.data_ptr()
