@@ -312,7 +312,16 @@ def run_b200(args, rank, world, local_rank):
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (workload, kernel) -> bytes; absent = not captured.
-NCU_TRAFFIC_BYTES: dict = {}
+NCU_TRAFFIC_BYTES: dict = {
+    # cfg3 launches = 4x the rows of the captured B=1, S=8192, window-128 case (traffic grows with rows)
+    ("cfg3", "fwd"): 4 * (83_966_720 + 30_039_296),
+    ("cfg3", "bwd_dkdv"): 4 * (155_233_792 + 12_281_600),
+    ("cfg3", "bwd_dq"): 4 * (155_229_952 + 42_418_944),
+    # cfg2 launches = 4x the rows of the captured B=1, S=4096 full-causal case
+    ("cfg2", "fwd"): 4 * (42_004_992 + 1_348_608),
+    ("cfg2", "bwd_dkdv"): 4 * (77_642_752 + 4_818_432),
+    ("cfg2", "bwd_dq"): 4 * (77_641_728 + 10_648_576),
+}
 
 
 # --------------------------------------------------------------------------------------------
