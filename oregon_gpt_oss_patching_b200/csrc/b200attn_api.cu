@@ -10,6 +10,7 @@
 #include "attn_common.cuh"
 #include "bwd_dkdv_kernel.cuh"
 #include "bwd_dq_kernel.cuh"
+#include "bwd_dq_small_kernel.cuh"
 #include "bwd_preprocess_kernel.cuh"
 #include "fwd_kernel.cuh"
 #include "umma_selftest.cuh"
@@ -242,12 +243,21 @@ int b200attn_bwd_dq(const b200attn_params* p) {
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
   CUtensorMap tk, tv;
+  const KernelArgs a = make_args(p);
+  dim3 grid(a.S_pad / kTile, p->Hq, p->B);
+  if (p->window > 0 && p->window <= kTile) {
+    // short key range (at most four 64-key blocks per query tile): the half-size kernel, two CTAs per SM
+    if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kBlk))) return rc;
+    if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kBlk))) return rc;
+    const size_t smem = sizeof(DqsSmem) + 1024;
+    if ((rc = set_smem(attn_bwd_dq_small_kernel, smem))) return rc;
+    attn_bwd_dq_small_kernel<<<grid, kDqsThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tk, tv, a);
+    return launch_status();
+  }
   if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
-  const KernelArgs a = make_args(p);
   const size_t smem = sizeof(DqSmem) + 1024;
   if ((rc = set_smem(attn_bwd_dq_kernel, smem))) return rc;
-  dim3 grid(a.S_pad / kTile, p->Hq, p->B);
   attn_bwd_dq_kernel<<<grid, kDqThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tk, tv, a);
   return launch_status();
 }
