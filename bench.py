@@ -372,6 +372,16 @@ NCU_TRAFFIC_BYTES: dict = {
 # --------------------------------------------------------------------------------------------
 # CPU arms (oracle port of the reference's eager path) -- the only place the oracle is executed
 # --------------------------------------------------------------------------------------------
+def use_all_host_threads() -> int:
+    """The CPU arms use every core this process may run on (torchrun sets OMP_NUM_THREADS=1 by default)."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_slices(case, n):
     units = [(b, g) for b in range(case.B) for g in range(case.Hkv)]
     return units[:max(1, min(n, len(units)))]
@@ -395,6 +405,7 @@ def cpu_sample(workload, budget_s=15.0):
     """Time the oracle port on a bounded number of (batch, KV-group) slices of the workload."""
     from oracle import CONFIGS, make_inputs
     case = CONFIGS[workload]
+    use_all_host_threads()
     tensors = make_inputs(case, dtype=torch.float32, device="cpu")
     one = cpu_slices(case, 1)
     t0 = time.perf_counter()
@@ -415,7 +426,9 @@ def run_reference(args, rank):
         return
     from oracle import CONFIGS, algorithmic_flops, make_inputs
     case = CONFIGS[args.workload]
+    use_all_host_threads()
     tensors = make_inputs(case, dtype=torch.float32, device="cpu")
+    cpu_step(case, tensors, cpu_slices(case, 1))   # first touch (allocator, thread pool)
     t0 = time.perf_counter()
     cpu_step(case, tensors, cpu_slices(case, 1))
     t_one = time.perf_counter() - t0
