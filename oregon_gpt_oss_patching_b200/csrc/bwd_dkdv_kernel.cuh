@@ -201,8 +201,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       while (ok && back < n_items) {
         bool progressed = false;
         // S^T/dP^T of item `front`: its stage has landed and the previous item's S^T/dP^T are in registers
-        if (front < n_items && mbar_try_wait(smem_u32(&sm->bar_in_full[front % kDkvStages]), (front / kDkvStages) & 1) &&
-            (front == 0 || mbar_try_wait(bar_s_free, (front - 1) & 1))) {
+        if (front < n_items && mbar_test_wait(smem_u32(&sm->bar_in_full[front % kDkvStages]), (front / kDkvStages) & 1) &&
+            (front == 0 || mbar_test_wait(bar_s_free, (front - 1) & 1))) {
           tc_fence_after_sync();
           const int s = front % kDkvStages;
           const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[s]));
@@ -218,7 +218,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
           progressed = true;
         }
         // dV/dK of item `back`: its P^T/dS^T have been written
-        if (back < front && mbar_try_wait(bar_p_full, back & 1)) {
+        if (back < front && mbar_test_wait(bar_p_full, back & 1)) {
           tc_fence_after_sync();
           const int s = back % kDkvStages;
           const uint64_t dot_desc = desc_mnmajor(smem_u32(sm->d_o[s]));

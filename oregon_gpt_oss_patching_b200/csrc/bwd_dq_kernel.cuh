@@ -175,8 +175,8 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       while (ok && back < n_items) {
         bool progressed = false;
         // S/dP of item `front`: its stage has landed and the previous item's S/dP are in registers
-        if (front < n_items && mbar_try_wait(smem_u32(&sm->bar_in_full[front % kDqStages]), (front / kDqStages) & 1) &&
-            (front == 0 || mbar_try_wait(bar_s_free, (front - 1) & 1))) {
+        if (front < n_items && mbar_test_wait(smem_u32(&sm->bar_in_full[front % kDqStages]), (front / kDqStages) & 1) &&
+            (front == 0 || mbar_test_wait(bar_s_free, (front - 1) & 1))) {
           tc_fence_after_sync();
           const int s = front % kDqStages;
           const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
@@ -192,7 +192,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
           progressed = true;
         }
         // dQ of item `back`: its dS has been written
-        if (back < front && mbar_try_wait(bar_p_full, back & 1)) {
+        if (back < front && mbar_test_wait(bar_p_full, back & 1)) {
           tc_fence_after_sync();
           const int s = back % kDqStages;
           const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));

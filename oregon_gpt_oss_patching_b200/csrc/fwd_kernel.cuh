@@ -228,10 +228,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         for (int x = 0; x < 2; ++x) {
           const int t = next_t[x];
           if (t >= nt) continue;
-          if (!mbar_try_wait(smem_u32(&sm->bar_p_full[x]), t & 1)) continue;
-          if (t >= 1 && !mbar_try_wait(smem_u32(&sm->bar_o_empty[x]), (t - 1) & 1)) continue;
+          if (!mbar_test_wait(smem_u32(&sm->bar_p_full[x]), t & 1)) continue;
+          if (t >= 1 && !mbar_test_wait(smem_u32(&sm->bar_o_empty[x]), (t - 1) & 1)) continue;
           const int sn = (t + 1) % kFwdStages;
-          if (t + 1 < nt && !mbar_try_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1)) continue;
+          if (t + 1 < nt && !mbar_test_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1)) continue;
           tc_fence_after_sync();
           const int s = t % kFwdStages;
           const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));

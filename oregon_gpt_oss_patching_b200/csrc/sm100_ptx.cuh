@@ -52,6 +52,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return done != 0;
 }
 
+// Non-blocking test (try_wait may suspend the thread for a while when the phase is not complete;
+// a loop that polls several barriers must not sit on one of them).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return done != 0;
+}
+
 constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s of SM clock: far beyond any legitimate wait
 
 // Bounded wait for the phase with the given parity to complete.  Returns false when the
