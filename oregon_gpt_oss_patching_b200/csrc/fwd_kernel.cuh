@@ -6,16 +6,20 @@
 // size only tile A is active.)  Per visible 128-key tile and per query tile:
 //     S = Q K^T                      tcgen05.mma, fp32 accumulator in tensor memory
 //     P = 2^(S*scale*log2e - m)      one thread per row, online softmax in registers
-//     O_tile = P V                   tcgen05.mma with P (bf16) as the A operand from tensor memory
-//     acc = acc * alpha + O_tile     in registers
-// The running maximum m starts at the head's sink logit; the sink joins the denominator in the
-// epilogue and carries no value.  Computes what the reference's `_attn_fwd` does
+//     O += P V                       tcgen05.mma with P (bf16) as the A operand from tensor memory,
+//                                    accumulating in tensor memory
+// The reference maximum m of a row starts at the head's sink logit and is only raised when the
+// row maximum has grown by more than 2^8 (the exponentials stay far inside the fp32/bf16 range and
+// the final normalisation uses the same m, so the result does not depend on when m is raised);
+// raising it rescales the row of O in tensor memory, which is rare after the first key tiles.
+// The sink joins the denominator in the epilogue and carries no value.  Computes what the reference's `_attn_fwd` does
 // (attention_kernel.py:11-100), in the log2 domain.  Key tiles that are entirely masked (above
 // the diagonal, left of the window, past the sequence end) are never loaded.
 //
 // Warp roles: warps 0-3 softmax of tile A, warps 4-7 softmax of tile B (thread r owns row r =
-// TMEM lane r), warp 8 lane 0 issues every MMA, warp 9 lane 0 issues every TMA load.  While one
-// tile's threads run their softmax the tensor core works for the other tile.
+// TMEM lane r), warp 8 lane 0 issues every MMA, warp 9 lane 0 issues every TMA load.  S of the
+// next key tile is issued as soon as the softmax threads have pulled the current S into registers,
+// so it is computed underneath the exponentials; P V follows when P is written.
 //
 // A softmax thread holds its whole 128-column row of S in registers (one burst of tensor-memory
 // loads per tile), so the row maximum, the exponentials and the row sum are computed without a
@@ -39,45 +43,54 @@ struct FwdSmem {
   alignas(8) uint64_t bar_q;
   uint64_t bar_kv_full[kFwdStages];
   uint64_t bar_kv_empty[kFwdStages];
-  uint64_t bar_s_full[2];   // S of tile X ready            (tcgen05.commit)
-  uint64_t bar_p_full[2];   // P of tile X written          (128 arrivals)
-  uint64_t bar_o_full[2];   // O_tile of tile X ready       (tcgen05.commit)
-  uint64_t bar_o_empty[2];  // O_tile of tile X consumed    (128 arrivals)
+  uint64_t bar_s_full[2];   // S of tile X ready                    (tcgen05.commit)
+  uint64_t bar_s_empty[2];  // S of tile X copied into registers    (128 arrivals)
+  uint64_t bar_p_full[2];   // P of tile X written                  (128 arrivals)
+  uint64_t bar_o_full[2];   // P V of tile X retired: P free, O current (tcgen05.commit)
   uint32_t tmem_base;
   int abort_flag;
   int loads_issued;         // K/V tile loads the loader has issued so far (for the abort drain)
 };
 
-// acc = acc * alpha + O_tile for the 64 output columns of this thread's row
-__device__ __forceinline__ void fwd_accumulate(float (&acc)[kHeadDim], uint32_t tmem_o_row, float alpha) {
+// O_row *= alpha for the 64 output columns of this thread's row, in tensor memory
+__device__ __forceinline__ void fwd_rescale_o(uint32_t tmem_o_row, float alpha) {
   uint32_t r0[32], r1[32];
   tmem_ld32(tmem_o_row, r0);
   tmem_ld32(tmem_o_row + 32, r1);
   tmem_wait_ld();
-  if (alpha == 1.f) {
 #pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      acc[e] += __uint_as_float(r0[e]);
-      acc[32 + e] += __uint_as_float(r1[e]);
-    }
-  } else {
-#pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      acc[e] = fmaf(acc[e], alpha, __uint_as_float(r0[e]));
-      acc[32 + e] = fmaf(acc[32 + e], alpha, __uint_as_float(r1[e]));
-    }
+  for (int e = 0; e < 32; ++e) {
+    r0[e] = __float_as_uint(__uint_as_float(r0[e]) * alpha);
+    r1[e] = __float_as_uint(__uint_as_float(r1[e]) * alpha);
   }
+  tmem_st32(tmem_o_row, r0);
+  tmem_st32(tmem_o_row + 32, r1);
+  tmem_wait_st();
 }
 
-// Softmax of one 128-column row held in registers: returns the new running maximum, writes
-// P (bf16) to tensor memory and adds the row sum.
+// Largest growth of the row maximum (log2 domain) tolerated before the reference maximum is raised.
+constexpr float kFwdRescaleThreshold = 8.f;
+
+struct FwdRowState {
+  float m;   // reference maximum of the exponents (log2 domain)
+  float l;   // running denominator without the sink, relative to m
+};
+
+// One key tile of one 128-column row: pulls S into registers (and releases the S columns), takes
+// the row maximum, raises the reference maximum when needed (rescaling O in tensor memory), writes
+// P = 2^(S*scale*log2e - m) as bf16 to tensor memory and adds the row sum.  `t` is the key-tile
+// counter of this query tile.  Returns false when a bounded wait was abandoned.
 template <bool kMask>
-__device__ __forceinline__ float fwd_softmax_row(uint32_t tmem_s_row, uint32_t tmem_p_row, float scale_log2, float m,
-                                                 int i, int kv0, int window, int len, float& rowsum) {
+__device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_t tmem_s_row, uint32_t tmem_p_row,
+                                                 uint32_t tmem_o_row, uint32_t bar_s_empty, uint32_t bar_o,
+                                                 float scale_log2, int i, int kv0, int window, int len,
+                                                 volatile int* abort_flag) {
   uint32_t s[4][32];
 #pragma unroll
   for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s_row + c * 32, s[c]);
   tmem_wait_ld();
+  tc_fence_before_sync();
+  mbar_arrive(bar_s_empty);   // the tensor core may overwrite S with the next key tile's scores
   if (kMask) {  // branch-free: one visibility bit mask per 32 keys, then selects
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
@@ -91,22 +104,40 @@ __device__ __forceinline__ float fwd_softmax_row(uint32_t tmem_s_row, uint32_t t
   for (int c = 0; c < 4; ++c)
 #pragma unroll
     for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(s[c][e]));
-  const float m_new = fmaxf(m, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2);
+  const float m_row = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+  // Raising m is a warp-wide decision (the tensor-memory accesses of the rescale are warp-collective).
+  if (t == 0) {
+    st.m = fmaxf(st.m, m_row);   // nothing accumulated yet: free
+  } else if (__any_sync(0xffffffffu, m_row - st.m > kFwdRescaleThreshold)) {
+    const float m_new = fmaxf(st.m, m_row);
+    const float alpha = fast_exp2(st.m - m_new);
+    st.m = m_new;
+    st.l *= alpha;
+    if (!warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag))) return false;   // P V of the previous tile retired
+    tc_fence_after_sync();
+    fwd_rescale_o(tmem_o_row, alpha);
+  }
+  const float m_ref = st.m;
   float sum[4] = {0.f, 0.f, 0.f, 0.f};
+  uint32_t pk[4][16];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
-    uint32_t pk[16];
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
-      const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][e]), scale_log2, -m_new));
-      const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][e + 1]), scale_log2, -m_new));
+      const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][e]), scale_log2, -m_ref));
+      const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][e + 1]), scale_log2, -m_ref));
       sum[(e >> 1) & 3] += p0 + p1;
-      pk[e >> 1] = pack_bf16(p0, p1);
+      pk[c][e >> 1] = pack_bf16(p0, p1);
     }
-    tmem_st16(tmem_p_row + c * 16, pk);
+    if (c == 0 && t > 0) {
+      // the P columns are free once P V of the previous key tile has retired
+      if (!warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag))) return false;
+      tc_fence_after_sync();
+    }
+    tmem_st16(tmem_p_row + c * 16, pk[c]);
   }
-  rowsum = (sum[0] + sum[1]) + (sum[2] + sum[3]);
-  return m_new;
+  st.l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+  return true;
 }
 
 __device__ __forceinline__ void setmaxnreg_inc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
@@ -154,9 +185,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(smem_u32(&sm->bar_s_full[x]), 1);
+      mbar_init(smem_u32(&sm->bar_s_empty[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_p_full[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_o_full[x]), 1);
-      mbar_init(smem_u32(&sm->bar_o_empty[x]), kComputeThreads);
     }
     sm->abort_flag = 0;
     sm->loads_issued = 0;
@@ -217,41 +248,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           umma_commit(smem_u32(&sm->bar_s_full[x]));
         }
       }
-      // Serve whichever tile has its P ready first, so that the two softmax warpgroups fall into
-      // anti-phase (one computes while the tensor core works for the other) instead of lockstep.
-      int next_t[2] = {0, n_act == 2 ? 0 : nt};   // next key tile whose P V is to be issued, per tile
+      // Serve whichever MMA has its operands ready first: S of the next key tile as soon as the
+      // softmax threads have emptied the S columns, P V as soon as P is written.  The two softmax
+      // warpgroups fall into anti-phase (one computes while the tensor core works for the other).
+      int next_s[2] = {1, n_act == 2 ? 1 : nt};    // next key tile whose S is to be issued, per query tile
+      int next_pv[2] = {0, n_act == 2 ? 0 : nt};   // next key tile whose P V is to be issued, per query tile
       long long t_idle0 = 0;
       uint32_t idle = 0;
-      while (ok && (next_t[0] < nt || next_t[1] < nt)) {
+      while (ok && (next_pv[0] < nt || next_pv[1] < nt)) {
         bool progressed = false;
 #pragma unroll
         for (int x = 0; x < 2; ++x) {
-          const int t = next_t[x];
-          if (t >= nt) continue;
-          if (!mbar_test_wait(smem_u32(&sm->bar_p_full[x]), t & 1)) continue;
-          if (t >= 1 && !mbar_test_wait(smem_u32(&sm->bar_o_empty[x]), (t - 1) & 1)) continue;
-          const int sn = (t + 1) % kFwdStages;
-          if (t + 1 < nt && !mbar_test_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1)) continue;
-          tc_fence_after_sync();
-          const int s = t % kFwdStages;
-          const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
-#pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ts(tmem + 384 + x * 64, tmem + 256 + x * 64 + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, kk > 0);
-          umma_commit(smem_u32(&sm->bar_o_full[x]));
-          // S of the next key tile goes behind P V in the pipe: when it is ready, P has been read
-          // and the softmax threads may overwrite the P columns.
-          if (t + 1 < nt) {
-            const uint64_t kn_desc = desc_kmajor(smem_u32(sm->k[sn]));
+          const int ts = next_s[x];
+          if (ts < nt && mbar_test_wait(smem_u32(&sm->bar_s_empty[x]), (ts - 1) & 1) &&
+              mbar_test_wait(smem_u32(&sm->bar_kv_full[ts % kFwdStages]), (ts / kFwdStages) & 1)) {
+            tc_fence_after_sync();
+            const uint64_t kn_desc = desc_kmajor(smem_u32(sm->k[ts % kFwdStages]));
 #pragma unroll
             for (int kk = 0; kk < kHeadDim / 16; ++kk)
               umma_ss(tmem + x * 128, q_desc[x] + kk * kDescKStepKMajor, kn_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
             umma_commit(smem_u32(&sm->bar_s_full[x]));
+            next_s[x] = ts + 1;
+            progressed = true;
           }
-          next_t[x] = t + 1;
-          // K[s], V[s] are free once both tiles' MMAs on them retire
-          if (next_t[x ^ 1] > t) umma_commit(smem_u32(&sm->bar_kv_empty[s]));
-          progressed = true;
+          const int t = next_pv[x];
+          if (t < nt && mbar_test_wait(smem_u32(&sm->bar_p_full[x]), t & 1)) {
+            tc_fence_after_sync();
+            const int s = t % kFwdStages;
+            const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
+#pragma unroll
+            for (int kk = 0; kk < kTile / 16; ++kk)
+              umma_ts(tmem + 384 + x * 64, tmem + 256 + x * 64 + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv,
+                      t > 0 || kk > 0);
+            umma_commit(smem_u32(&sm->bar_o_full[x]));
+            next_pv[x] = t + 1;
+            // K[s], V[s] are free once both tiles' MMAs on them retire
+            if (next_pv[x ^ 1] > t) umma_commit(smem_u32(&sm->bar_kv_empty[s]));
+            progressed = true;
+          }
         }
         if (progressed) {
           idle = 0;
@@ -279,55 +313,51 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     const uint32_t tmem_s_row = tmem + x * 128 + lane_addr;
     const uint32_t tmem_p_row = tmem + 256 + x * 64 + lane_addr;
     const uint32_t tmem_o_row = tmem + 384 + x * 64 + lane_addr;
-    const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_p = smem_u32(&sm->bar_p_full[x]),
-                   bar_o = smem_u32(&sm->bar_o_full[x]), bar_oe = smem_u32(&sm->bar_o_empty[x]);
+    const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
+                   bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]);
     const float sink2 = a.sinks[h] * kLog2e;
-    float m = sink2;         // reference maximum of the exponents (log2 domain), starts at the sink logit
-    float l = 0.f;           // running denominator without the sink, relative to m
-    float alpha = 1.f;       // rescale factor of the latest key tile
-    float acc[kHeadDim];
-#pragma unroll
-    for (int c = 0; c < kHeadDim; ++c) acc[c] = 0.f;
+    FwdRowState st{sink2, 0.f};   // the reference maximum starts at the sink logit
     bool ok = true;
 
     for (int t = 0; t < nt; ++t) {
       const int kv0 = (t_first + t) * kTile;
       const bool need_mask = tile_needs_mask(q0, kv0, a.window, len);
       if (!(ok = warp_all(mbar_wait(bar_s, t & 1, abort_flag)))) break;
-      if (t > 0) {
-        // P V of the previous key tile retired before this S did: fold it in first
-        if (!(ok = warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag)))) break;
-        tc_fence_after_sync();
-        fwd_accumulate(acc, tmem_o_row, alpha);
-        tc_fence_before_sync();
-        mbar_arrive(bar_oe);
-      }
       tc_fence_after_sync();
-      float rowsum;
-      const float m_new = need_mask
-          ? fwd_softmax_row<true>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, rowsum)
-          : fwd_softmax_row<false>(tmem_s_row, tmem_p_row, a.scale_log2, m, i, kv0, a.window, len, rowsum);
-      alpha = fast_exp2(m - m_new);
-      m = m_new;
+      ok = need_mask
+          ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, a.scale_log2, i, kv0,
+                                   a.window, len, abort_flag)
+          : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, a.scale_log2, i, kv0,
+                                    a.window, len, abort_flag);
+      if (!ok) break;
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar_p);
-      l = l * alpha + rowsum;
     }
     if (ok) ok = warp_all(mbar_wait(bar_o, (nt - 1) & 1, abort_flag));
     if (ok) {
       tc_fence_after_sync();
-      fwd_accumulate(acc, tmem_o_row, alpha);
-      const float z = l + fast_exp2(sink2 - m);   // the sink joins the denominator only
+      uint32_t o0[32], o1[32];
+      tmem_ld32(tmem_o_row, o0);
+      tmem_ld32(tmem_o_row + 32, o1);
+      tmem_wait_ld();
+      const float z = st.l + fast_exp2(sink2 - st.m);   // the sink joins the denominator only
       const float inv = 1.f / z;
       if (i < a.S) {
         __nv_bfloat16* dst = a.o.row(b, h, i);
 #pragma unroll
-        for (int c = 0; c < kHeadDim; c += 8)
-          store_bf16x8(dst + c, pack_bf16(acc[c] * inv, acc[c + 1] * inv), pack_bf16(acc[c + 2] * inv, acc[c + 3] * inv),
-                       pack_bf16(acc[c + 4] * inv, acc[c + 5] * inv), pack_bf16(acc[c + 6] * inv, acc[c + 7] * inv));
+        for (int c = 0; c < 32; c += 8) {
+          store_bf16x8(dst + c, pack_bf16(__uint_as_float(o0[c]) * inv, __uint_as_float(o0[c + 1]) * inv),
+                       pack_bf16(__uint_as_float(o0[c + 2]) * inv, __uint_as_float(o0[c + 3]) * inv),
+                       pack_bf16(__uint_as_float(o0[c + 4]) * inv, __uint_as_float(o0[c + 5]) * inv),
+                       pack_bf16(__uint_as_float(o0[c + 6]) * inv, __uint_as_float(o0[c + 7]) * inv));
+          store_bf16x8(dst + 32 + c, pack_bf16(__uint_as_float(o1[c]) * inv, __uint_as_float(o1[c + 1]) * inv),
+                       pack_bf16(__uint_as_float(o1[c + 2]) * inv, __uint_as_float(o1[c + 3]) * inv),
+                       pack_bf16(__uint_as_float(o1[c + 4]) * inv, __uint_as_float(o1[c + 5]) * inv),
+                       pack_bf16(__uint_as_float(o1[c + 6]) * inv, __uint_as_float(o1[c + 7]) * inv));
+        }
       }
-      a.lse[((long long)(b * a.Hq + h)) * a.S_pad + i] = (i < len) ? (m + log2f(z)) * kLn2 : 0.f;
+      a.lse[((long long)(b * a.Hq + h)) * a.S_pad + i] = (i < len) ? (st.m + log2f(z)) * kLn2 : 0.f;
     }
   }
   }

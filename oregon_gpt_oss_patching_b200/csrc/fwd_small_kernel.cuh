@@ -8,9 +8,31 @@
 // second CTA fill those gaps.  Both key tiles get their own shared-memory stage (no ring).
 #pragma once
 #include "attn_common.cuh"
-#include "fwd_kernel.cuh"  // fwd_accumulate
+#include "attn_common.cuh"
 
 namespace b200attn {
+
+// acc = acc * alpha + O_tile for the 64 output columns of this thread's row
+__device__ __forceinline__ void fwd_accumulate(float (&acc)[kHeadDim], uint32_t tmem_o_row, float alpha) {
+  uint32_t r0[32], r1[32];
+  tmem_ld32(tmem_o_row, r0);
+  tmem_ld32(tmem_o_row + 32, r1);
+  tmem_wait_ld();
+  if (alpha == 1.f) {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      acc[e] += __uint_as_float(r0[e]);
+      acc[32 + e] += __uint_as_float(r1[e]);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 32; ++e) {
+      acc[e] = fmaf(acc[e], alpha, __uint_as_float(r0[e]));
+      acc[32 + e] = fmaf(acc[32 + e], alpha, __uint_as_float(r1[e]));
+    }
+  }
+}
+
 
 constexpr int kFwdsStages = 2;      // = the most key tiles a launch of this kernel may need per query tile
 constexpr int kFwdsThreads = 256;
