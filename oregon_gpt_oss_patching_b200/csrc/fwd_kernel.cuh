@@ -17,22 +17,22 @@
 // the diagonal, left of the window, past the sequence end) are never loaded.
 //
 // Warp roles: warps 0-3 softmax of tile A, warps 4-7 softmax of tile B (thread r owns row r =
-// TMEM lane r), warp 8 lane 0 issues every MMA, warp 9 lane 0 issues every TMA load.  S of the
+// TMEM lane r), warp 8 lane 0 issues tile A's MMAs, warp 10 lane 0 tile B's, warp 9 lane 0 every TMA load.  S of the
 // next key tile is issued as soon as the softmax threads have pulled the current S into registers,
 // so it is computed underneath the exponentials; P V follows when P is written.
 //
 // A softmax thread holds its whole 128-column row of S in registers (one burst of tensor-memory
 // loads per tile), so the row maximum, the exponentials and the row sum are computed without a
 // second read.  The register file is re-partitioned with setmaxnreg: the two softmax warpgroups
-// take 224 registers per thread, the warpgroup holding the MMA and TMA warps keeps 56
-// (2*128*224 + 128*56 = 384*168, the pool the CTA is launched with).
+// take 208 registers per thread, the warpgroup holding the MMA and TMA warps keeps 88
+// (2*128*208 + 128*88 = 384*168, the pool the CTA is launched with; with fewer the MMA warp spills).
 #pragma once
 #include "attn_common.cuh"
 
 namespace b200attn {
 
 constexpr int kFwdStages = 3;
-constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax A, softmax B, {MMA warp, TMA warp, 2 idle warps}
+constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax A, softmax B, {MMA warp A, TMA warp, MMA warp B, idle warp}
 constexpr int kFwdTmemCols = 512;
 // tensor-memory columns: S_A [0,128) S_B [128,256) P_A [256,320) P_B [320,384) O_A [384,448) O_B [448,512)
 
@@ -76,10 +76,57 @@ struct FwdRowState {
   float l;   // running denominator without the sink, relative to m
 };
 
-// One key tile of one 128-column row: pulls S into registers (and releases the S columns), takes
-// the row maximum, raises the reference maximum when needed (rescaling O in tensor memory), writes
-// P = 2^(S*scale*log2e - m) as bf16 to tensor memory and adds the row sum.  `t` is the key-tile
-// counter of this query tile.  Returns false when a bounded wait was abandoned.
+__device__ __forceinline__ float fwd_row_max(const uint32_t (&s)[4][32]) {
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+  for (int c = 0; c < 4; ++c)
+#pragma unroll
+    for (int e = 0; e < 32; e += 2)
+      mx[(e >> 1) & 3] = fmax3(mx[(e >> 1) & 3], __uint_as_float(s[c][e]), __uint_as_float(s[c][e + 1]));
+  return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+}
+
+// P = 2^(S*scale*log2e - m_ref) of one row: written as bf16 to tensor memory, row sum and (when kWithMax)
+// row maximum of S returned.  Exponentials, sum, packing and maximum are interleaved element by
+// element (packed fp32 pairs where the hardware has them), so that the special-function unit, the
+// bottleneck, is fed from the first instruction to the last instead of idling during a separate
+// maximum pass.  `wait_bar` != 0: the P columns are free once that barrier's phase completes.
+template <bool kWithMax>
+__device__ __forceinline__ bool fwd_exp_row(const uint32_t (&s)[4][32], float scale_log2, float m_ref, uint32_t tmem_p_row,
+                                            uint32_t wait_bar, uint32_t wait_parity, volatile int* abort_flag,
+                                            float& rowsum, float& rowmax) {
+  float2 sum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  const float2 scale2 = make_float2(scale_log2, scale_log2), neg_m2 = make_float2(-m_ref, -m_ref);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    uint32_t pk[16];
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      const float s0 = __uint_as_float(s[c][e]), s1 = __uint_as_float(s[c][e + 1]);
+      const float2 x = __ffma2_rn(make_float2(s0, s1), scale2, neg_m2);
+      const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+      sum[(e >> 1) & 3] = __fadd2_rn(sum[(e >> 1) & 3], p);
+      pk[e >> 1] = pack_bf16(p.x, p.y);
+      if (kWithMax) mx[(e >> 1) & 3] = fmax3(mx[(e >> 1) & 3], s0, s1);
+    }
+    if (c == 0 && wait_bar != 0u) {
+      if (!warp_all(mbar_wait(wait_bar, wait_parity, abort_flag))) return false;
+      tc_fence_after_sync();
+    }
+    tmem_st16(tmem_p_row + c * 16, pk);
+  }
+  rowsum = ((sum[0].x + sum[0].y) + (sum[1].x + sum[1].y)) + ((sum[2].x + sum[2].y) + (sum[3].x + sum[3].y));
+  rowmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+  return true;
+}
+
+// One key tile of one 128-column row: pulls S into registers (and releases the S columns), writes
+// P as bf16 to tensor memory and adds the row sum.  After the first key tile the exponentials are
+// taken against the current reference maximum right away, with the row maximum computed alongside;
+// only when the row maximum turns out to exceed the reference by more than the threshold (rare) is the
+// reference raised, the row of O in tensor memory rescaled and the row of P recomputed.  `t` is the
+// key-tile counter of this query tile.  Returns false when a bounded wait was abandoned.
 template <bool kMask>
 __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_t tmem_s_row, uint32_t tmem_p_row,
                                                  uint32_t tmem_o_row, uint32_t bar_s_empty, uint32_t bar_o,
@@ -99,49 +146,32 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
       for (int e = 0; e < 32; ++e) s[c][e] = (bits >> e) & 1u ? s[c][e] : 0xff800000u;  // -inf
     }
   }
-  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-  for (int c = 0; c < 4; ++c)
-#pragma unroll
-    for (int e = 0; e < 32; ++e) mx[e & 3] = fmaxf(mx[e & 3], __uint_as_float(s[c][e]));
-  const float m_row = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
-  // Raising m is a warp-wide decision (the tensor-memory accesses of the rescale are warp-collective).
+  float rowsum, rowmax;
   if (t == 0) {
-    st.m = fmaxf(st.m, m_row);   // nothing accumulated yet: free
-  } else if (__any_sync(0xffffffffu, m_row - st.m > kFwdRescaleThreshold)) {
-    const float m_new = fmaxf(st.m, m_row);
-    const float alpha = fast_exp2(st.m - m_new);
-    st.m = m_new;
-    st.l *= alpha;
-    if (!warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag))) return false;   // P V of the previous tile retired
-    tc_fence_after_sync();
-    fwd_rescale_o(tmem_o_row, alpha);
-  }
-  const float m_ref = st.m;
-  float sum[4] = {0.f, 0.f, 0.f, 0.f};
-  uint32_t pk[4][16];
-#pragma unroll
-  for (int c = 0; c < 4; ++c) {
-#pragma unroll
-    for (int e = 0; e < 32; e += 2) {
-      const float p0 = fast_exp2(fmaf(__uint_as_float(s[c][e]), scale_log2, -m_ref));
-      const float p1 = fast_exp2(fmaf(__uint_as_float(s[c][e + 1]), scale_log2, -m_ref));
-      sum[(e >> 1) & 3] += p0 + p1;
-      pk[c][e >> 1] = pack_bf16(p0, p1);
+    // nothing accumulated yet: adopt the row maximum first (the reference starts at the sink logit)
+    st.m = fmaxf(st.m, fwd_row_max(s) * scale_log2);
+    if (!fwd_exp_row<false>(s, scale_log2, st.m, tmem_p_row, 0u, 0u, abort_flag, rowsum, rowmax)) return false;
+  } else {
+    // the P columns are free once P V of the previous key tile has retired
+    if (!fwd_exp_row<true>(s, scale_log2, st.m, tmem_p_row, bar_o, (t - 1) & 1, abort_flag, rowsum, rowmax)) return false;
+    const float m_row = rowmax * scale_log2;
+    // Raising m is a warp-wide decision (the tensor-memory accesses of the rescale are warp-collective).
+    if (__any_sync(0xffffffffu, m_row - st.m > kFwdRescaleThreshold)) {
+      const float m_new = fmaxf(st.m, m_row);
+      const float alpha = fast_exp2(st.m - m_new);
+      st.m = m_new;
+      st.l *= alpha;
+      tmem_wait_st();
+      fwd_rescale_o(tmem_o_row, alpha);   // P V of the previous tile has retired (waited for above)
+      if (!fwd_exp_row<false>(s, scale_log2, st.m, tmem_p_row, 0u, 0u, abort_flag, rowsum, rowmax)) return false;
     }
-    if (c == 0 && t > 0) {
-      // the P columns are free once P V of the previous key tile has retired
-      if (!warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag))) return false;
-      tc_fence_after_sync();
-    }
-    tmem_st16(tmem_p_row + c * 16, pk[c]);
   }
-  st.l += (sum[0] + sum[1]) + (sum[2] + sum[3]);
+  st.l += rowsum;
   return true;
 }
 
-__device__ __forceinline__ void setmaxnreg_inc_224() { asm volatile("setmaxnreg.inc.sync.aligned.u32 224;"); }
-__device__ __forceinline__ void setmaxnreg_dec_56() { asm volatile("setmaxnreg.dec.sync.aligned.u32 56;"); }
+__device__ __forceinline__ void setmaxnreg_inc_208() { asm volatile("setmaxnreg.inc.sync.aligned.u32 208;"); }
+__device__ __forceinline__ void setmaxnreg_dec_88() { asm volatile("setmaxnreg.dec.sync.aligned.u32 88;"); }
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -181,7 +211,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar_q, 1);
     for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(smem_u32(&sm->bar_kv_full[s]), 1);
-      mbar_init(smem_u32(&sm->bar_kv_empty[s]), 1);
+      mbar_init(smem_u32(&sm->bar_kv_empty[s]), n_act);   // one tcgen05.commit per active query tile
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(smem_u32(&sm->bar_s_full[x]), 1);
@@ -204,7 +234,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem = sm->tmem_base;
 
   if (warp >= 8) {
-  setmaxnreg_dec_56();
+  setmaxnreg_dec_88();
 
   if (warp == 9) {
     // ------------------------------------ TMA loader ------------------------------------
@@ -229,72 +259,45 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     }
     __syncwarp();
-  } else if (warp == 8) {
-    // ------------------------------------ MMA issuer ------------------------------------
-    if (lane == 0) {
+  } else if (warp == 8 || warp == 10) {
+    // ----------------------- MMA issuer of tile A (warp 8) / tile B (warp 10) -----------------------
+    // One issuing thread per query tile, on different SM sub-partitions: tcgen05.mma issue is
+    // synchronous with the tensor pipe and an issuing warp gets few issue slots next to busy softmax
+    // warps, so one thread for both tiles would serialise the two tiles' chains.
+    const int x = (warp - 8) >> 1;
+    if (lane == 0 && x < n_act) {
       const uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, 0, 1);
-      uint64_t q_desc[2];
-      for (int x = 0; x < 2; ++x) q_desc[x] = desc_kmajor(smem_u32(sm->q[x]));
+      const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[x]));
+      const uint32_t tmem_s = tmem + x * 128, tmem_p = tmem + 256 + x * 64, tmem_o = tmem + 384 + x * 64;
+      const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
+                     bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]);
       bool ok = mbar_wait(bar_q, 0, abort_flag);
-      if (ok) ok = mbar_wait(smem_u32(&sm->bar_kv_full[0]), 0, abort_flag);
-      if (ok) {
-        tc_fence_after_sync();
-        const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[0]));
-        for (int x = 0; x < n_act; ++x) {
+      for (int t = -1; ok && t < nt; ++t) {
+        // S of key tile t+1: as soon as the softmax threads have emptied the S columns (copied S of
+        // tile t into registers), so that it is computed underneath their exponentials
+        if (t + 1 < nt) {
+          const int sn = (t + 1) % kFwdStages;
+          if (t >= 0 && !(ok = mbar_wait(bar_se, t & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[sn]));
 #pragma unroll
           for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ss(tmem + x * 128, q_desc[x] + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
-          umma_commit(smem_u32(&sm->bar_s_full[x]));
+            umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
+          umma_commit(bar_s);
         }
-      }
-      // Serve whichever MMA has its operands ready first: S of the next key tile as soon as the
-      // softmax threads have emptied the S columns, P V as soon as P is written.  The two softmax
-      // warpgroups fall into anti-phase (one computes while the tensor core works for the other).
-      int next_s[2] = {1, n_act == 2 ? 1 : nt};    // next key tile whose S is to be issued, per query tile
-      int next_pv[2] = {0, n_act == 2 ? 0 : nt};   // next key tile whose P V is to be issued, per query tile
-      long long t_idle0 = 0;
-      uint32_t idle = 0;
-      while (ok && (next_pv[0] < nt || next_pv[1] < nt)) {
-        bool progressed = false;
+        // O += P V of key tile t: as soon as P is written
+        if (t >= 0) {
+          if (!(ok = mbar_wait(bar_p, t & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const int s = t % kFwdStages;
+          const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
 #pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          const int ts = next_s[x];
-          if (ts < nt && mbar_test_wait(smem_u32(&sm->bar_s_empty[x]), (ts - 1) & 1) &&
-              mbar_test_wait(smem_u32(&sm->bar_kv_full[ts % kFwdStages]), (ts / kFwdStages) & 1)) {
-            tc_fence_after_sync();
-            const uint64_t kn_desc = desc_kmajor(smem_u32(sm->k[ts % kFwdStages]));
-#pragma unroll
-            for (int kk = 0; kk < kHeadDim / 16; ++kk)
-              umma_ss(tmem + x * 128, q_desc[x] + kk * kDescKStepKMajor, kn_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
-            umma_commit(smem_u32(&sm->bar_s_full[x]));
-            next_s[x] = ts + 1;
-            progressed = true;
-          }
-          const int t = next_pv[x];
-          if (t < nt && mbar_test_wait(smem_u32(&sm->bar_p_full[x]), t & 1)) {
-            tc_fence_after_sync();
-            const int s = t % kFwdStages;
-            const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
-#pragma unroll
-            for (int kk = 0; kk < kTile / 16; ++kk)
-              umma_ts(tmem + 384 + x * 64, tmem + 256 + x * 64 + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv,
-                      t > 0 || kk > 0);
-            umma_commit(smem_u32(&sm->bar_o_full[x]));
-            next_pv[x] = t + 1;
-            // K[s], V[s] are free once both tiles' MMAs on them retire
-            if (next_pv[x ^ 1] > t) umma_commit(smem_u32(&sm->bar_kv_empty[s]));
-            progressed = true;
-          }
-        }
-        if (progressed) {
-          idle = 0;
-        } else if ((++idle & 1023u) == 0u) {   // bounded: give up after ~2 s without progress
-          if (idle == 1024u) t_idle0 = clock64();
-          if (*abort_flag || clock64() - t_idle0 > kWaitLimitCycles) {
-            sm->abort_flag = 1;
-            ok = false;
-          }
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, t > 0 || kk > 0);
+          umma_commit(bar_o);
+          umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // K[s], V[s] are free once every tile's MMAs on them retire
         }
       }
       if (!ok) report_abort(a);
@@ -302,7 +305,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
   }
   } else {
-  setmaxnreg_inc_224();
+  setmaxnreg_inc_208();
   if (warp < 4 * n_act) {
     // -------------------------------------- softmax --------------------------------------
     const int x = warp >> 2;                                      // tile A or B
