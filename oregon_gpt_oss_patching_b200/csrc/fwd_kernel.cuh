@@ -24,8 +24,8 @@
 // A softmax thread holds its whole 128-column row of S in registers (one burst of tensor-memory
 // loads per tile), so the row maximum, the exponentials and the row sum are computed without a
 // second read.  The register file is re-partitioned with setmaxnreg: the two softmax warpgroups
-// take 208 registers per thread, the warpgroup holding the MMA and TMA warps keeps 88
-// (2*128*208 + 128*88 = 384*168, the pool the CTA is launched with; with fewer the MMA warp spills).
+// take 216 registers per thread, the warpgroup holding the MMA and TMA warps keeps 72
+// (2*128*216 + 128*72 = 384*168, the pool the CTA is launched with).
 #pragma once
 #include "attn_common.cuh"
 
@@ -47,6 +47,7 @@ struct FwdSmem {
   uint64_t bar_s_empty[2];  // S of tile X copied into registers    (128 arrivals)
   uint64_t bar_p_full[2];   // P of tile X written                  (128 arrivals)
   uint64_t bar_o_full[2];   // P V of tile X retired: P free, O current (tcgen05.commit)
+  uint64_t bar_exp[2];      // tile X may run its exponentials       (128 arrivals of the other tile)
   uint32_t tmem_base;
   int abort_flag;
   int loads_issued;         // K/V tile loads the loader has issued so far (for the abort drain)
@@ -86,92 +87,126 @@ __device__ __forceinline__ float fwd_row_max(const uint32_t (&s)[4][32]) {
   return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-// P = 2^(S*scale*log2e - m_ref) of one row: written as bf16 to tensor memory, row sum and (when kWithMax)
-// row maximum of S returned.  Exponentials, sum, packing and maximum are interleaved element by
-// element (packed fp32 pairs where the hardware has them), so that the special-function unit, the
-// bottleneck, is fed from the first instruction to the last instead of idling during a separate
-// maximum pass.  `wait_bar` != 0: the P columns are free once that barrier's phase completes.
+// Visibility mask of one 32-key chunk applied to S in registers (branch-free: bit mask, then selects).
+__device__ __forceinline__ void fwd_mask_chunk(uint32_t (&sc)[32], int i, int j0, int window, int len) {
+  const uint32_t bits = visible_keys32(i, j0, window, len);
+#pragma unroll
+  for (int e = 0; e < 32; ++e) sc[e] = (bits >> e) & 1u ? sc[e] : 0xff800000u;  // -inf
+}
+
+// P = 2^(S*scale*log2e - m_ref) of one 32-key chunk of a row: packed to bf16, row sum and (when
+// kWithMax) row maximum of S accumulated.  Exponentials, sum, packing and maximum are interleaved
+// element by element (packed fp32 pairs where the hardware has them), so that the special-function
+// unit, the bottleneck, is fed all the time instead of idling during a separate maximum pass.
 template <bool kWithMax>
-__device__ __forceinline__ bool fwd_exp_row(const uint32_t (&s)[4][32], float scale_log2, float m_ref, uint32_t tmem_p_row,
-                                            uint32_t wait_bar, uint32_t wait_parity, volatile int* abort_flag,
-                                            float& rowsum, float& rowmax) {
-  float2 sum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-  const float2 scale2 = make_float2(scale_log2, scale_log2), neg_m2 = make_float2(-m_ref, -m_ref);
+__device__ __forceinline__ void fwd_exp_chunk(const uint32_t (&sc)[32], float2 scale2, float2 neg_m2, uint32_t (&pk)[16],
+                                              float2 (&sum)[4], float (&mx)[4]) {
 #pragma unroll
-  for (int c = 0; c < 4; ++c) {
-    uint32_t pk[16];
-#pragma unroll
-    for (int e = 0; e < 32; e += 2) {
-      const float s0 = __uint_as_float(s[c][e]), s1 = __uint_as_float(s[c][e + 1]);
-      const float2 x = __ffma2_rn(make_float2(s0, s1), scale2, neg_m2);
-      const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-      sum[(e >> 1) & 3] = __fadd2_rn(sum[(e >> 1) & 3], p);
-      pk[e >> 1] = pack_bf16(p.x, p.y);
-      if (kWithMax) mx[(e >> 1) & 3] = fmax3(mx[(e >> 1) & 3], s0, s1);
-    }
-    if (c == 0 && wait_bar != 0u) {
-      if (!warp_all(mbar_wait(wait_bar, wait_parity, abort_flag))) return false;
-      tc_fence_after_sync();
-    }
-    tmem_st16(tmem_p_row + c * 16, pk);
+  for (int e = 0; e < 32; e += 2) {
+    const float s0 = __uint_as_float(sc[e]), s1 = __uint_as_float(sc[e + 1]);
+    const float2 x = __ffma2_rn(make_float2(s0, s1), scale2, neg_m2);
+    const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+    sum[(e >> 1) & 3] = __fadd2_rn(sum[(e >> 1) & 3], p);
+    pk[e >> 1] = pack_bf16(p.x, p.y);
+    if (kWithMax) mx[(e >> 1) & 3] = fmax3(mx[(e >> 1) & 3], s0, s1);
   }
-  rowsum = ((sum[0].x + sum[0].y) + (sum[1].x + sum[1].y)) + ((sum[2].x + sum[2].y) + (sum[3].x + sum[3].y));
-  rowmax = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-  return true;
+}
+
+__device__ __forceinline__ float fwd_sum4(const float2 (&sum)[4]) {
+  return ((sum[0].x + sum[0].y) + (sum[1].x + sum[1].y)) + ((sum[2].x + sum[2].y) + (sum[3].x + sum[3].y));
 }
 
 // One key tile of one 128-column row: pulls S into registers (and releases the S columns), writes
 // P as bf16 to tensor memory and adds the row sum.  After the first key tile the exponentials are
-// taken against the current reference maximum right away, with the row maximum computed alongside;
-// only when the row maximum turns out to exceed the reference by more than the threshold (rare) is the
-// reference raised, the row of O in tensor memory rescaled and the row of P recomputed.  `t` is the
+// taken against the current reference maximum right away, 32 keys at a time while the next 32
+// scores are on their way from tensor memory, with the row maximum computed alongside; only when
+// the row maximum turns out to exceed the reference by more than the threshold (rare) is the
+// reference raised: the row of O in tensor memory and this tile's P (already bf16) are multiplied
+// by 2^(old - new).  P is stored only after the whole row is done, when P V of the previous key tile
+// has certainly left the P columns, so the softmax threads never stand waiting for the tensor core.  `t` is the
 // key-tile counter of this query tile.  Returns false when a bounded wait was abandoned.
 template <bool kMask>
 __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_t tmem_s_row, uint32_t tmem_p_row,
                                                  uint32_t tmem_o_row, uint32_t bar_s_empty, uint32_t bar_o,
+                                                 uint32_t bar_exp_mine, uint32_t exp_parity, uint32_t bar_exp_other,
                                                  float scale_log2, int i, int kv0, int window, int len,
                                                  volatile int* abort_flag) {
   uint32_t s[4][32];
+  const float2 scale2 = make_float2(scale_log2, scale_log2);
+  float2 sum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
+  float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+  if (t == 0) {
+    // nothing accumulated yet: take the whole row, adopt its maximum (the reference starts at the
+    // sink logit), then the exponentials
 #pragma unroll
-  for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s_row + c * 32, s[c]);
-  tmem_wait_ld();
-  tc_fence_before_sync();
-  mbar_arrive(bar_s_empty);   // the tensor core may overwrite S with the next key tile's scores
-  if (kMask) {  // branch-free: one visibility bit mask per 32 keys, then selects
+    for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s_row + c * 32, s[c]);
+    tmem_wait_ld();
+    tc_fence_before_sync();
+    mbar_arrive(bar_s_empty);   // the tensor core may overwrite S with the next key tile's scores
+    if (kMask) {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) fwd_mask_chunk(s[c], i, kv0 + c * 32, window, len);
+    }
+    st.m = fmaxf(st.m, fwd_row_max(s) * scale_log2);
+    const float2 neg_m2 = make_float2(-st.m, -st.m);
+    if (bar_exp_mine != 0u && !warp_all(mbar_wait(bar_exp_mine, exp_parity, abort_flag))) return false;
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
-      const uint32_t bits = visible_keys32(i, kv0 + c * 32, window, len);
-#pragma unroll
-      for (int e = 0; e < 32; ++e) s[c][e] = (bits >> e) & 1u ? s[c][e] : 0xff800000u;  // -inf
+      uint32_t pk[16];
+      if (c == 3 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);
+      fwd_exp_chunk<false>(s[c], scale2, neg_m2, pk, sum, mx);
+      tmem_st16(tmem_p_row + c * 16, pk);
     }
-  }
-  float rowsum, rowmax;
-  if (t == 0) {
-    // nothing accumulated yet: adopt the row maximum first (the reference starts at the sink logit)
-    st.m = fmaxf(st.m, fwd_row_max(s) * scale_log2);
-    if (!fwd_exp_row<false>(s, scale_log2, st.m, tmem_p_row, 0u, 0u, abort_flag, rowsum, rowmax)) return false;
   } else {
-    // the P columns are free once P V of the previous key tile has retired
-    if (!fwd_exp_row<true>(s, scale_log2, st.m, tmem_p_row, bar_o, (t - 1) & 1, abort_flag, rowsum, rowmax)) return false;
-    const float m_row = rowmax * scale_log2;
+    const float2 neg_m2 = make_float2(-st.m, -st.m);
+    uint32_t pk[4][16];
+    tmem_ld32(tmem_s_row, s[0]);
+    tmem_wait_ld();
+    // The exponentials of the two query tiles take turns (bar_exp_mine == 0: single tile, no turns):
+    // the special-function unit is the bottleneck, and a tile that has it to itself finishes its row
+    // while the other tile stores P, waits for its next S and loads it, instead of both tiles
+    // crawling through the exponentials in lockstep and then both leaving the unit idle.
+    if (bar_exp_mine != 0u && !warp_all(mbar_wait(bar_exp_mine, exp_parity, abort_flag))) return false;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      if (c < 3) tmem_ld32(tmem_s_row + (c + 1) * 32, s[c + 1]);   // in flight under this chunk's exponentials
+      if (c == 3 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);   // hand over a little early: covers the wake-up latency
+      if (kMask) fwd_mask_chunk(s[c], i, kv0 + c * 32, window, len);
+      fwd_exp_chunk<true>(s[c], scale2, neg_m2, pk[c], sum, mx);
+      if (c < 3) tmem_wait_ld();
+      if (c == 2) {
+        tc_fence_before_sync();
+        mbar_arrive(bar_s_empty);   // the whole row is in registers: S of the next key tile may be computed
+      }
+    }
+    const float m_row = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
+    // P V of the previous key tile has long retired by now: the P columns are free and O is current
+    if (!warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag))) return false;
+    tc_fence_after_sync();
     // Raising m is a warp-wide decision (the tensor-memory accesses of the rescale are warp-collective).
     if (__any_sync(0xffffffffu, m_row - st.m > kFwdRescaleThreshold)) {
       const float m_new = fmaxf(st.m, m_row);
       const float alpha = fast_exp2(st.m - m_new);
       st.m = m_new;
-      st.l *= alpha;
-      tmem_wait_st();
-      fwd_rescale_o(tmem_o_row, alpha);   // P V of the previous tile has retired (waited for above)
-      if (!fwd_exp_row<false>(s, scale_log2, st.m, tmem_p_row, 0u, 0u, abort_flag, rowsum, rowmax)) return false;
+      st.l = (st.l + fwd_sum4(sum)) * alpha;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) sum[k] = make_float2(0.f, 0.f);
+      fwd_rescale_o(tmem_o_row, alpha);
+      const uint32_t alpha2 = pack_bf16(alpha, alpha);
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+#pragma unroll
+        for (int k = 0; k < 16; ++k) pk[c][k] = mul_bf16x2(pk[c][k], alpha2);   // P of this tile, moved to the new reference
     }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) tmem_st16(tmem_p_row + c * 16, pk[c]);
   }
-  st.l += rowsum;
+  st.l += fwd_sum4(sum);
   return true;
 }
 
-__device__ __forceinline__ void setmaxnreg_inc_208() { asm volatile("setmaxnreg.inc.sync.aligned.u32 208;"); }
-__device__ __forceinline__ void setmaxnreg_dec_88() { asm volatile("setmaxnreg.dec.sync.aligned.u32 88;"); }
+__device__ __forceinline__ void setmaxnreg_inc_216_fwd() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
+__device__ __forceinline__ void setmaxnreg_dec_72_fwd() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
 
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
@@ -218,6 +253,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&sm->bar_s_empty[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_p_full[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_o_full[x]), 1);
+      mbar_init(smem_u32(&sm->bar_exp[x]), kComputeThreads);
     }
     sm->abort_flag = 0;
     sm->loads_issued = 0;
@@ -234,7 +270,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem = sm->tmem_base;
 
   if (warp >= 8) {
-  setmaxnreg_dec_88();
+  setmaxnreg_dec_72_fwd();
 
   if (warp == 9) {
     // ------------------------------------ TMA loader ------------------------------------
@@ -305,7 +341,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     __syncwarp();
   }
   } else {
-  setmaxnreg_inc_208();
+  setmaxnreg_inc_216_fwd();
   if (warp < 4 * n_act) {
     // -------------------------------------- softmax --------------------------------------
     const int x = warp >> 2;                                      // tile A or B
@@ -320,6 +356,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                    bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]);
     const float sink2 = a.sinks[h] * kLog2e;
     FwdRowState st{sink2, 0.f};   // the reference maximum starts at the sink logit
+    const uint32_t bar_exp_mine = n_act == 2 ? smem_u32(&sm->bar_exp[x]) : 0u;
+    const uint32_t bar_exp_other = n_act == 2 ? smem_u32(&sm->bar_exp[x ^ 1]) : 0u;
     bool ok = true;
 
     for (int t = 0; t < nt; ++t) {
@@ -327,11 +365,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const bool need_mask = tile_needs_mask(q0, kv0, a.window, len);
       if (!(ok = warp_all(mbar_wait(bar_s, t & 1, abort_flag)))) break;
       tc_fence_after_sync();
+      // tile A goes first: its first wait (parity 1 of a fresh barrier) passes at once
+      const uint32_t exp_parity = (x == 0) ? ((t & 1) ^ 1) : (t & 1);
       ok = need_mask
-          ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, a.scale_log2, i, kv0,
-                                   a.window, len, abort_flag)
-          : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, a.scale_log2, i, kv0,
-                                    a.window, len, abort_flag);
+          ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, bar_exp_mine, exp_parity,
+                                   bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag)
+          : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, bar_exp_mine, exp_parity,
+                                    bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag);
       if (!ok) break;
       tmem_wait_st();
       tc_fence_before_sync();
