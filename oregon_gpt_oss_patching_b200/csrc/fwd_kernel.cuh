@@ -153,7 +153,7 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t pk[16];
-      if (c == 3 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);
+      if (c == 2 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);
       fwd_exp_chunk<false>(s[c], scale2, neg_m2, pk, sum, mx);
       tmem_st16(tmem_p_row + c * 16, pk);
     }
@@ -170,7 +170,7 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       if (c < 3) tmem_ld32(tmem_s_row + (c + 1) * 32, s[c + 1]);   // in flight under this chunk's exponentials
-      if (c == 3 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);   // hand over a little early: covers the wake-up latency
+      if (c == 2 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);   // hand over early: covers the wake-up latency
       if (kMask) fwd_mask_chunk(s[c], i, kv0 + c * 32, window, len);
       fwd_exp_chunk<true>(s[c], scale2, neg_m2, pk[c], sum, mx);
       if (c < 3) tmem_wait_ld();
