@@ -20,8 +20,8 @@
 //
 // Q and dO (the A operands of S and dP for the CTA's whole life) are copied once into tensor
 // memory as bf16, so those MMAs read only the K/V tile from shared memory.  Pipeline as in the
-// dK/dV kernel: warp 9 streams K/V tiles through a 3-stage TMA ring, warp 8 issues every MMA
-// from a first-ready service loop, the two compute warpgroups split the 128 key columns of an
+// dK/dV kernel: warp 9 streams K/V tiles through a 3-stage TMA ring, warp 8 issues the S/dP MMAs
+// and warp 10 the dQ MMAs, the two compute warpgroups split the 128 key columns of an
 // item, pull their half of S/dP into registers and release those columns at once (the tensor
 // core computes the next item's S/dP under this item's exponentials), and write dS to its own
 // columns once the previous item's dQ MMAs have left them.  Every wait is bounded.
@@ -57,25 +57,29 @@ template <bool kMask>
 __device__ __forceinline__ void dq_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], float scale_log2,
                                            float nl2, float delta, int i, int j0, int window, int len,
                                            uint32_t (&pk)[2][16], float& pdp) {
-  float acc0 = 0.f, acc1 = 0.f;
+  // two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
+  // slots, should be what the row waits for -- the MMA-issuing warps live on the slots left over
+  float2 acc = make_float2(0.f, 0.f);
+  const float2 scale2 = make_float2(scale_log2, scale_log2), nl22 = make_float2(nl2, nl2);
+  const float2 neg_delta2 = make_float2(-delta, -delta);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     const uint32_t bits = kMask ? visible_keys32(i, j0 + c * 32, window, len) : 0xffffffffu;
 #pragma unroll
     for (int e = 0; e < 32; e += 2) {
-      float p0 = fast_exp2(fmaf(__uint_as_float(rs[c][e]), scale_log2, nl2));
-      float p1 = fast_exp2(fmaf(__uint_as_float(rs[c][e + 1]), scale_log2, nl2));
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[c][e]), __uint_as_float(rs[c][e + 1])), scale2, nl22);
+      float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
       if (kMask) {  // selects, not branches
-        p0 = (bits >> e) & 1u ? p0 : 0.f;
-        p1 = (bits >> (e + 1)) & 1u ? p1 : 0.f;
+        p.x = (bits >> e) & 1u ? p.x : 0.f;
+        p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
       }
-      const float dp0 = __uint_as_float(rp[c][e]), dp1 = __uint_as_float(rp[c][e + 1]);
-      acc0 = fmaf(p0, dp0, acc0);
-      acc1 = fmaf(p1, dp1, acc1);
-      pk[c][e >> 1] = pack_bf16(p0 * (dp0 - delta), p1 * (dp1 - delta));
+      const float2 dp = make_float2(__uint_as_float(rp[c][e]), __uint_as_float(rp[c][e + 1]));
+      acc = __ffma2_rn(p, dp, acc);
+      const float2 ds = __fmul2_rn(p, __fadd2_rn(dp, neg_delta2));
+      pk[c][e >> 1] = pack_bf16(ds.x, ds.y);
     }
   }
-  pdp += acc0 + acc1;
+  pdp += acc.x + acc.y;
 }
 
 __global__ void __launch_bounds__(kDqThreads, 1)
@@ -163,57 +167,48 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
     __syncwarp();
   } else if (warp == 8) {
-    // ------------------------------------ MMA issuer ------------------------------------
+    // ------------------------- MMA issuer, S and dP (front) -------------------------
+    // tcgen05.mma issue is synchronous with the tensor pipe, and an issuing warp gets few issue
+    // slots next to busy compute warps: front and back MMAs have an issuing warp each, on different
+    // SM sub-partitions, so that neither waits behind the other's issue.
     if (lane == 0) {
       const uint32_t idesc_front = make_idesc_bf16(kTile, kTile, 0, 0);    // A in TMEM, B K-contiguous, N = 128
-      const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
       bool ok = mbar_wait(bar_q, 0, abort_flag);
-      tc_fence_after_sync();
-      int front = 0, back = 0;  // next item whose S/dP resp. dQ MMAs are to be issued
-      long long t_idle0 = 0;
-      uint32_t idle = 0;
-      while (ok && back < n_items) {
-        bool progressed = false;
-        // S/dP of item `front`: its stage has landed and the previous item's S/dP are in registers
-        if (front < n_items && mbar_test_wait(smem_u32(&sm->bar_in_full[front % kDqStages]), (front / kDqStages) & 1) &&
-            (front == 0 || mbar_test_wait(bar_s_free, (front - 1) & 1))) {
-          tc_fence_after_sync();
-          const int s = front % kDqStages;
-          const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
-          const uint64_t v_desc = desc_kmajor(smem_u32(sm->v[s]));
+      for (int it = 0; ok && it < n_items; ++it) {
+        // the stage has landed and the previous item's S/dP are in registers
+        const int s = it % kDqStages;
+        if (!(ok = mbar_wait(smem_u32(&sm->bar_in_full[s]), (it / kDqStages) & 1, abort_flag))) break;
+        if (it > 0 && !(ok = mbar_wait(bar_s_free, (it - 1) & 1, abort_flag))) break;
+        tc_fence_after_sync();
+        const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
+        const uint64_t v_desc = desc_kmajor(smem_u32(sm->v[s]));
 #pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ts(tmem_s, tmem_q + kk * 8, k_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          umma_ts(tmem_s, tmem_q + kk * 8, k_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
 #pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ts(tmem_dp, tmem_do + kk * 8, v_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
-          umma_commit(bar_s_full);
-          ++front;
-          progressed = true;
-        }
-        // dQ of item `back`: its dS has been written
-        if (back < front && mbar_test_wait(bar_p_full, back & 1)) {
-          tc_fence_after_sync();
-          const int s = back % kDqStages;
-          const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          umma_ts(tmem_dp, tmem_do + kk * 8, v_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+        umma_commit(bar_s_full);
+      }
+      if (!ok) report_abort(a);
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ------------------------------ MMA issuer, dQ (back) ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
+      bool ok = true;
+      for (int it = 0; ok && it < n_items; ++it) {
+        if (!(ok = mbar_wait(bar_p_full, it & 1, abort_flag))) break;   // dS of the item has been written
+        tc_fence_after_sync();
+        const int s = it % kDqStages;
+        const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ts(tmem_dq, tmem_ds + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, (back > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(bar_p_free);                      // dS columns reusable once these retire
-          umma_commit(smem_u32(&sm->bar_in_empty[s]));  // and so is the K/V stage
-          if (back == n_items - 1) umma_commit(bar_acc);
-          ++back;
-          progressed = true;
-        }
-        if (progressed) {
-          idle = 0;
-        } else if ((++idle & 1023u) == 0u) {  // bounded: give up after ~2 s without progress
-          if (idle == 1024u) t_idle0 = clock64();
-          if (*abort_flag || clock64() - t_idle0 > kWaitLimitCycles) {
-            sm->abort_flag = 1;
-            ok = false;
-          }
-        }
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts(tmem_dq, tmem_ds + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar_p_free);                      // dS columns reusable once these retire
+        umma_commit(smem_u32(&sm->bar_in_empty[s]));  // and so is the K/V stage (its S/dP MMAs retired before dS was written)
+        if (it == n_items - 1) umma_commit(bar_acc);
       }
       if (!ok) report_abort(a);
     }
