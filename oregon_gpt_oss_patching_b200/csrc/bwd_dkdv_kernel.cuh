@@ -12,7 +12,7 @@
 // atomics, attention_kernel.py:201-212).
 //
 // Pipeline.  Warp 9 streams Q/dO tiles (+ the LSE and delta rows) through a 3-stage TMA ring.
-// Warp 8 issues every MMA from a first-ready service loop.  The two compute warpgroups split
+// Warp 8 issues the S^T/dP^T MMAs and warp 10 the dV/dK MMAs.  The two compute warpgroups split
 // the 128 query columns of an item (warps 0-3: columns 0-63, warps 4-7: columns 64-127), pull
 // their half of S^T/dP^T into registers and release those columns at once, so the tensor core
 // computes S^T/dP^T of the next item while the exponentials of this one are still running;
@@ -64,8 +64,11 @@ template <bool kMask>
 __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], const float* nlse,
                                             const float* delta, float scale_log2, int i0, int j, int window, int len,
                                             uint32_t (&pp)[2][16], uint32_t (&pd)[2][16]) {
+  // two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
+  // slots, should be what the row waits for -- the MMA-issuing warps live on the slots left over
   const float4* nl4 = reinterpret_cast<const float4*>(nlse);
   const float4* de4 = reinterpret_cast<const float4*>(delta);
+  const float2 scale2 = make_float2(scale_log2, scale_log2), neg1 = make_float2(-1.f, -1.f);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     const uint32_t bits = kMask ? visible_queries32(j, i0 + c * 32, window, len) : 0xffffffffu;
@@ -73,20 +76,22 @@ __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const u
     for (int e4 = 0; e4 < 8; ++e4) {
       const float4 L = nl4[c * 8 + e4];
       const float4 D = de4[c * 8 + e4];
-      const float lv[4] = {L.x, L.y, L.z, L.w};
-      const float dl[4] = {D.x, D.y, D.z, D.w};
-      float p[4], ds[4];
+      const float2 lv[2] = {make_float2(L.x, L.y), make_float2(L.z, L.w)};
+      const float2 dl[2] = {make_float2(D.x, D.y), make_float2(D.z, D.w)};
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int e = e4 * 4 + u;
-        p[u] = fast_exp2(fmaf(__uint_as_float(rs[c][e]), scale_log2, lv[u]));
-        if (kMask) p[u] = (bits >> e) & 1u ? p[u] : 0.f;  // select, not a branch
-        ds[u] = p[u] * (__uint_as_float(rp[c][e]) - dl[u]);
+      for (int u = 0; u < 2; ++u) {
+        const int e = e4 * 4 + u * 2;
+        const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[c][e]), __uint_as_float(rs[c][e + 1])), scale2, lv[u]);
+        float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+        if (kMask) {  // selects, not branches
+          p.x = (bits >> e) & 1u ? p.x : 0.f;
+          p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
+        }
+        const float2 dp = make_float2(__uint_as_float(rp[c][e]), __uint_as_float(rp[c][e + 1]));
+        const float2 ds = __fmul2_rn(p, __ffma2_rn(dl[u], neg1, dp));   // P * (dP - delta)
+        pp[c][e4 * 2 + u] = pack_bf16(p.x, p.y);
+        pd[c][e4 * 2 + u] = pack_bf16(ds.x, ds.y);
       }
-      pp[c][e4 * 2] = pack_bf16(p[0], p[1]);
-      pp[c][e4 * 2 + 1] = pack_bf16(p[2], p[3]);
-      pd[c][e4 * 2] = pack_bf16(ds[0], ds[1]);
-      pd[c][e4 * 2 + 1] = pack_bf16(ds[2], ds[3]);
     }
   }
 }
@@ -188,62 +193,54 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     }
     __syncwarp();
   } else if (warp == 8) {
-    // ------------------------------------ MMA issuer ------------------------------------
+    // ------------------------ MMA issuer, S^T and dP^T (front) ------------------------
+    // tcgen05.mma issue is synchronous with the tensor pipe, and an issuing warp gets few issue
+    // slots next to busy compute warps: front and back MMAs have an issuing warp each, on different
+    // SM sub-partitions, so that neither waits behind the other's issue.
     if (lane == 0) {
       const uint32_t idesc_front = make_idesc_bf16(kTile, kTile, 0, 0);    // A, B both K-contiguous, N = 128
-      const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
       const uint64_t k_desc = desc_kmajor(smem_u32(sm->k));
       const uint64_t v_desc = desc_kmajor(smem_u32(sm->v));
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
-      int front = 0, back = 0;  // next item whose S^T/dP^T resp. dV/dK MMAs are to be issued
-      long long t_idle0 = 0;
-      uint32_t idle = 0;
-      while (ok && back < n_items) {
-        bool progressed = false;
-        // S^T/dP^T of item `front`: its stage has landed and the previous item's S^T/dP^T are in registers
-        if (front < n_items && mbar_test_wait(smem_u32(&sm->bar_in_full[front % kDkvStages]), (front / kDkvStages) & 1) &&
-            (front == 0 || mbar_test_wait(bar_s_free, (front - 1) & 1))) {
-          tc_fence_after_sync();
-          const int s = front % kDkvStages;
-          const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[s]));
-          const uint64_t do_desc = desc_kmajor(smem_u32(sm->d_o[s]));
+      for (int it = 0; ok && it < n_items; ++it) {
+        // the stage has landed and the previous item's S^T/dP^T are in registers
+        const int s = it % kDkvStages;
+        if (!(ok = mbar_wait(smem_u32(&sm->bar_in_full[s]), (it / kDkvStages) & 1, abort_flag))) break;
+        if (it > 0 && !(ok = mbar_wait(bar_s_free, (it - 1) & 1, abort_flag))) break;
+        tc_fence_after_sync();
+        const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[s]));
+        const uint64_t do_desc = desc_kmajor(smem_u32(sm->d_o[s]));
 #pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ss(tmem_st, k_desc + kk * kDescKStepKMajor, q_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          umma_ss(tmem_st, k_desc + kk * kDescKStepKMajor, q_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
 #pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ss(tmem_dpt, v_desc + kk * kDescKStepKMajor, do_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
-          umma_commit(bar_s_full);
-          ++front;
-          progressed = true;
-        }
-        // dV/dK of item `back`: its P^T/dS^T have been written
-        if (back < front && mbar_test_wait(bar_p_full, back & 1)) {
-          tc_fence_after_sync();
-          const int s = back % kDkvStages;
-          const uint64_t dot_desc = desc_mnmajor(smem_u32(sm->d_o[s]));
-          const uint64_t qt_desc = desc_mnmajor(smem_u32(sm->q[s]));
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          umma_ss(tmem_dpt, v_desc + kk * kDescKStepKMajor, do_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+        umma_commit(bar_s_full);
+      }
+      if (!ok) report_abort(a);
+    }
+    __syncwarp();
+  } else if (warp == 10) {
+    // ---------------------------- MMA issuer, dV and dK (back) ----------------------------
+    if (lane == 0) {
+      const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
+      bool ok = true;
+      for (int it = 0; ok && it < n_items; ++it) {
+        if (!(ok = mbar_wait(bar_p_full, it & 1, abort_flag))) break;   // P^T/dS^T of the item have been written
+        tc_fence_after_sync();
+        const int s = it % kDkvStages;
+        const uint64_t dot_desc = desc_mnmajor(smem_u32(sm->d_o[s]));
+        const uint64_t qt_desc = desc_mnmajor(smem_u32(sm->q[s]));
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ts(tmem_dv, tmem_pt + kk * 8, dot_desc + kk * kDescKStepMNMajor, idesc_back, (back > 0 || kk > 0) ? 1u : 0u);
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts(tmem_dv, tmem_pt + kk * 8, dot_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ts(tmem_dk, tmem_dst + kk * 8, qt_desc + kk * kDescKStepMNMajor, idesc_back, (back > 0 || kk > 0) ? 1u : 0u);
-          umma_commit(bar_p_free);                      // P^T/dS^T columns reusable once these retire
-          umma_commit(smem_u32(&sm->bar_in_empty[s]));  // and so is the Q/dO stage
-          if (back == n_items - 1) umma_commit(bar_acc);
-          ++back;
-          progressed = true;
-        }
-        if (progressed) {
-          idle = 0;
-        } else if ((++idle & 1023u) == 0u) {  // bounded: give up after ~2 s without progress
-          if (idle == 1024u) t_idle0 = clock64();
-          if (*abort_flag || clock64() - t_idle0 > kWaitLimitCycles) {
-            sm->abort_flag = 1;
-            ok = false;
-          }
-        }
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts(tmem_dk, tmem_dst + kk * 8, qt_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(bar_p_free);                      // P^T/dS^T columns reusable once these retire
+        umma_commit(smem_u32(&sm->bar_in_empty[s]));  // and so is the Q/dO stage (its S^T/dP^T MMAs retired before P^T was written)
+        if (it == n_items - 1) umma_commit(bar_acc);
       }
       if (!ok) report_abort(a);
     }
