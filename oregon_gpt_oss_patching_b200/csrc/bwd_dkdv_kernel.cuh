@@ -69,13 +69,22 @@ __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const u
   const float4* nl4 = reinterpret_cast<const float4*>(nlse);
   const float4* de4 = reinterpret_cast<const float4*>(delta);
   const float2 scale2 = make_float2(scale_log2, scale_log2), neg1 = make_float2(-1.f, -1.f);
+  float4 Lq[4], Dq[4];
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
     const uint32_t bits = kMask ? visible_queries32(j, i0 + c * 32, window, len) : 0xffffffffu;
 #pragma unroll
     for (int e4 = 0; e4 < 8; ++e4) {
-      const float4 L = nl4[c * 8 + e4];
-      const float4 D = de4[c * 8 + e4];
+      // the per-column constants of 16 columns at a time, fetched ahead of the arithmetic that uses them
+      if ((e4 & 3) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          Lq[q] = nl4[c * 8 + e4 + q];
+          Dq[q] = de4[c * 8 + e4 + q];
+        }
+      }
+      const float4 L = Lq[e4 & 3];
+      const float4 D = Dq[e4 & 3];
       const float2 lv[2] = {make_float2(L.x, L.y), make_float2(L.z, L.w)};
       const float2 dl[2] = {make_float2(D.x, D.y), make_float2(D.z, D.w)};
 #pragma unroll
@@ -255,9 +264,10 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
     bool ok = true;
 
-    for (int it = 0; it < n_items; ++it) {
+    int qi = 0;   // query tile of the item within its head (items run over the head's tiles, then the next head)
+    for (int it = 0; it < n_items; ++it, qi = (qi + 1 == nq) ? 0 : qi + 1) {
       const int s = it % kDkvStages;
-      const int i0 = dkv_item(it, nq, qt_first, g, a.group).q0 + wg * 64;  // first query column of this thread
+      const int i0 = (qt_first + qi) * kTile + wg * 64;  // first query column of this thread
       const bool need_mask = (kv0 + kTile - 1 > i0) || (a.window != 0 && kv0 <= i0 + 63 - a.window) || (i0 + 64 > len);
       // nlse/delta of this stage are read with plain loads below: observe their barrier directly
       if (!(ok = warp_all(mbar_wait(smem_u32(&sm->bar_in_full[s]), (it / kDkvStages) & 1, abort_flag)))) break;
