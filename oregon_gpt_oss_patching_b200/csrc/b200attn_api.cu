@@ -191,18 +191,14 @@ int b200attn_fwd(const b200attn_params* p) {
   if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
-  if (p->window > 0 && p->window <= kTile) {
-    // short key range (at most two key tiles per query tile): the half-size kernel, two CTAs per SM
-    const size_t smem = sizeof(FwdsSmem) + 1024;
-    if ((rc = set_smem(attn_fwd_small_kernel, smem))) return rc;
-    dim3 grid(a.S_pad / kTile, p->Hq, p->B);
-    attn_fwd_small_kernel<<<grid, kFwdsThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
-    return launch_status();
-  }
   const size_t smem = sizeof(FwdSmem) + 1024;
   if ((rc = set_smem(attn_fwd_kernel, smem))) return rc;
-  const int heads_per_cta = (a.group % 2 == 0) ? 2 : 1;  // two heads of a KV group share staged K/V tiles
-  dim3 grid(a.S_pad / kTile, p->Hq / heads_per_cta, p->B);
+  int n_sm = 0;
+  if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
+  const int heads_per_item = (a.group % 2 == 0) ? 2 : 1;  // two heads of a KV group share staged K/V tiles
+  const long long n_items = (long long)(a.S_pad / kTile) * p->B * (p->Hq / heads_per_item);
+  // persistent: one CTA per SM walks the work items
+  const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);
   attn_fwd_kernel<<<grid, kFwdThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
   return launch_status();
 }

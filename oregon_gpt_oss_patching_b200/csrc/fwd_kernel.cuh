@@ -1,6 +1,6 @@
 // Forward attention kernel for sm_100a.
 //
-// One CTA = one 128-row query tile of TWO query heads of the same KV group (tile A and tile
+// One work item = one 128-row query tile of TWO query heads of the same KV group (tile A and tile
 // B), so that every K/V tile staged in shared memory by TMA feeds two heads; the other heads
 // of the group run in neighbouring CTAs and find the same K/V tiles in L2.  (With an odd group
 // size only tile A is active.)  Per visible 128-key tile and per query tile:
@@ -37,20 +37,23 @@ constexpr int kFwdTmemCols = 512;
 // tensor-memory columns: S_A [0,128) S_B [128,256) P_A [256,320) P_B [320,384) O_A [384,448) O_B [448,512)
 
 struct FwdSmem {
-  alignas(1024) uint8_t q[2][kTileBytes];
+  alignas(1024) uint8_t q[2][2][kTileBytes];   // [buffer][query tile A/B]: the next work item's Q lands while this one runs
   alignas(1024) uint8_t k[kFwdStages][kTileBytes];
   alignas(1024) uint8_t v[kFwdStages][kTileBytes];
-  alignas(8) uint64_t bar_q;
+  alignas(8) uint64_t bar_q_full[2];   // Q of a buffer landed
+  uint64_t bar_q_empty[2];             // every S MMA reading a Q buffer retired   (tcgen05.commit per tile)
   uint64_t bar_kv_full[kFwdStages];
   uint64_t bar_kv_empty[kFwdStages];
   uint64_t bar_s_full[2];   // S of tile X ready                    (tcgen05.commit)
   uint64_t bar_s_empty[2];  // S of tile X copied into registers    (128 arrivals)
   uint64_t bar_p_full[2];   // P of tile X written                  (128 arrivals)
   uint64_t bar_o_full[2];   // P V of tile X retired: P free, O current (tcgen05.commit)
+  uint64_t bar_o_free[2];   // O of tile X read by the epilogue     (128 arrivals)
   uint64_t bar_exp[2];      // tile X may run its exponentials       (128 arrivals of the other tile)
   uint32_t tmem_base;
   int abort_flag;
   int loads_issued;         // K/V tile loads the loader has issued so far (for the abort drain)
+  int q_loads_issued;       // Q loads (work items) issued so far
 };
 
 // O_row *= alpha for the 64 output columns of this thread's row, in tensor memory
@@ -124,11 +127,12 @@ __device__ __forceinline__ float fwd_sum4(const float2 (&sum)[4]) {
 // reference raised: the row of O in tensor memory and this tile's P (already bf16) are multiplied
 // by 2^(old - new).  P is stored only after the whole row is done, when P V of the previous key tile
 // has certainly left the P columns, so the softmax threads never stand waiting for the tensor core.  `t` is the
-// key-tile counter of this query tile.  Returns false when a bounded wait was abandoned.
+// key-tile counter of this query tile, `prev_parity` the phase of bar_o that the previous key tile's
+// P V completes.  Returns false when a bounded wait was abandoned.
 template <bool kMask>
 __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_t tmem_s_row, uint32_t tmem_p_row,
                                                  uint32_t tmem_o_row, uint32_t bar_s_empty, uint32_t bar_o,
-                                                 uint32_t bar_exp_mine, uint32_t exp_parity, uint32_t bar_exp_other,
+                                                 uint32_t prev_parity, uint32_t bar_exp_mine, uint32_t exp_parity, uint32_t bar_exp_other,
                                                  float scale_log2, int i, int kv0, int window, int len,
                                                  volatile int* abort_flag) {
   uint32_t s[4][32];
@@ -181,7 +185,7 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
     }
     const float m_row = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * scale_log2;
     // P V of the previous key tile has long retired by now: the P columns are free and O is current
-    if (!warp_all(mbar_wait(bar_o, (t - 1) & 1, abort_flag))) return false;
+    if (!warp_all(mbar_wait(bar_o, prev_parity, abort_flag))) return false;
     tc_fence_after_sync();
     // Raising m is a warp-wide decision (the tensor-memory accesses of the rescale are warp-collective).
     if (__any_sync(0xffffffffu, m_row - st.m > kFwdRescaleThreshold)) {
@@ -208,6 +212,54 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
 __device__ __forceinline__ void setmaxnreg_inc_216_fwd() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
 __device__ __forceinline__ void setmaxnreg_dec_72_fwd() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
 
+// One unit of work: one 128-row query tile of n_act (1 or 2) query heads of one KV group.
+struct FwdItem {
+  int b, h0, g, q0, len, t_first, nt;   // nt = visible key tiles; 0 = the tile is padding only
+};
+__device__ __forceinline__ FwdItem fwd_item(const KernelArgs& a, int id, int n_act) {
+  const int n_hp = a.Hq / n_act, n_qt = a.S_pad / kTile, per_qt = a.B * n_hp;
+  const int qt = n_qt - 1 - id / per_qt;   // long (late) query tiles first; neighbouring ids share K/V in L2
+  const int rem = id % per_qt;
+  FwdItem it;
+  it.b = rem / n_hp;
+  it.h0 = (rem % n_hp) * n_act;
+  it.g = it.h0 / a.group;
+  it.q0 = qt * kTile;
+  it.len = seq_len(a, it.b);
+  if (it.q0 >= it.len) {
+    it.t_first = 0;
+    it.nt = 0;
+  } else {
+    const int hi = min(it.q0 + kTile - 1, it.len - 1);               // last visible key
+    const int lo = a.window ? max(0, it.q0 - a.window + 1) : 0;      // first visible key
+    it.t_first = lo / kTile;
+    it.nt = hi / kTile - it.t_first + 1;
+  }
+  return it;
+}
+// Work item of this CTA's round k: rounds alternate direction (0, 1, .., G-1, then G-1, .., 0), so
+// that with items sorted by decreasing length every CTA gets nearly the same total.
+__device__ __forceinline__ int fwd_item_id(int k) {
+  const int c = (k & 1) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  return k * (int)gridDim.x + c;
+}
+// first round at or after `k` whose work item exists and has key tiles; false if none
+__device__ __forceinline__ bool fwd_next_item(const KernelArgs& a, int& k, int n_items, int n_act, FwdItem& it) {
+  const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  for (; k < n_rounds; ++k) {
+    const int id = fwd_item_id(k);
+    if (id >= n_items) continue;
+    it = fwd_item(a, id, n_act);
+    if (it.nt > 0) return true;
+  }
+  return false;
+}
+
+// Persistent: the grid is one CTA per SM and every CTA walks the work items id = blockIdx.x,
+// blockIdx.x + gridDim.x, ...  Barriers, tensor memory and the TMA rings are set up once; the loader
+// runs ahead across item boundaries (Q is double-buffered), and S of an item's first key tile is
+// issued before P V of the previous item's last one, so the per-item set-up and first-load latency
+// that dominate short (sliding-window) items are hidden behind the previous item's work.
 __global__ void __launch_bounds__(kFwdThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
@@ -217,33 +269,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const int tid = threadIdx.x;
   const int warp = tid >> 5;
   const int lane = tid & 31;
-  const int b = blockIdx.z;
-  const int n_act = (a.group % 2 == 0) ? 2 : 1;   // query heads (tiles) handled by this CTA
-  const int h0 = blockIdx.y * n_act;
-  const int g = h0 / a.group;
-  const int qt = gridDim.x - 1 - blockIdx.x;      // long (late) tiles first
-  const int q0 = qt * kTile;
-  const int len = seq_len(a, b);
-
-  if (q0 >= len) {  // tile is padding only: define its output, no tensor work
-    if (tid < n_act * kComputeThreads) {
-      const int x = tid >> 7, r = tid & 127;
-      if (q0 + r < a.S) zero_row(a.o.row(b, h0 + x, q0 + r));
-      a.lse[((long long)(b * a.Hq + h0 + x)) * a.S_pad + q0 + r] = 0.f;
-    }
-    return;
-  }
-
-  const int hi = min(q0 + kTile - 1, len - 1);              // last visible key
-  const int lo = a.window ? max(0, q0 - a.window + 1) : 0;  // first visible key
-  const int t_first = lo / kTile;
-  const int nt = hi / kTile - t_first + 1;
-
-  const uint32_t bar_q = smem_u32(&sm->bar_q);
+  const int n_act = (a.group % 2 == 0) ? 2 : 1;   // query heads (tiles) handled per work item
+  const int n_items = (a.S_pad / kTile) * a.B * (a.Hq / n_act);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
-    mbar_init(bar_q, 1);
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(smem_u32(&sm->bar_q_full[q]), 1);
+      mbar_init(smem_u32(&sm->bar_q_empty[q]), n_act);    // one tcgen05.commit per active query tile
+    }
     for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(smem_u32(&sm->bar_kv_full[s]), 1);
       mbar_init(smem_u32(&sm->bar_kv_empty[s]), n_act);   // one tcgen05.commit per active query tile
@@ -253,10 +287,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(smem_u32(&sm->bar_s_empty[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_p_full[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_o_full[x]), 1);
+      mbar_init(smem_u32(&sm->bar_o_free[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_exp[x]), kComputeThreads);
     }
     sm->abort_flag = 0;
     sm->loads_issued = 0;
+    sm->q_loads_issued = 0;
     fence_mbar_init();
   }
   if (warp == 8) {
@@ -278,21 +314,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       prefetch_tmap(&tm_q);
       prefetch_tmap(&tm_k);
       prefetch_tmap(&tm_v);
-      mbar_arrive_expect_tx(bar_q, n_act * kTileBytes);
-      for (int x = 0; x < n_act; ++x) tma_load_4d(smem_u32(sm->q[x]), &tm_q, bar_q, 0, q0, h0 + x, b);
-      for (int t = 0; t < nt; ++t) {
-        const int s = t % kFwdStages;
-        if (t >= kFwdStages && !mbar_wait(smem_u32(&sm->bar_kv_empty[s]), ((t / kFwdStages) - 1) & 1, abort_flag)) {
-          report_abort(a);
-          break;
+      int kq = 0;   // work items with key tiles so far (Q buffer = kq & 1)
+      int T = 0;    // key tiles so far (stage = T % kFwdStages)
+      bool ok = true;
+      FwdItem it;
+      for (int k = 0; ok && fwd_next_item(a, k, n_items, n_act, it); ++k, ++kq) {
+        const int qb = kq & 1;
+        if (kq >= 2 && !(ok = mbar_wait(smem_u32(&sm->bar_q_empty[qb]), ((kq >> 1) - 1) & 1, abort_flag))) break;
+        const uint32_t bar_q = smem_u32(&sm->bar_q_full[qb]);
+        mbar_arrive_expect_tx(bar_q, n_act * kTileBytes);
+        for (int x = 0; x < n_act; ++x) tma_load_4d(smem_u32(sm->q[qb][x]), &tm_q, bar_q, 0, it.q0, it.h0 + x, it.b);
+        *reinterpret_cast<volatile int*>(&sm->q_loads_issued) = kq + 1;
+        for (int t = 0; t < it.nt; ++t, ++T) {
+          const int s = T % kFwdStages;
+          if (T >= kFwdStages && !(ok = mbar_wait(smem_u32(&sm->bar_kv_empty[s]), ((T / kFwdStages) - 1) & 1, abort_flag))) break;
+          const int kv0 = (it.t_first + t) * kTile;
+          const uint32_t bar = smem_u32(&sm->bar_kv_full[s]);
+          mbar_arrive_expect_tx(bar, 2 * kTileBytes);
+          tma_load_4d(smem_u32(sm->k[s]), &tm_k, bar, 0, kv0, it.g, it.b);
+          tma_load_4d(smem_u32(sm->v[s]), &tm_v, bar, 0, kv0, it.g, it.b);
+          *reinterpret_cast<volatile int*>(&sm->loads_issued) = T + 1;
         }
-        const int kv0 = (t_first + t) * kTile;
-        const uint32_t bar = smem_u32(&sm->bar_kv_full[s]);
-        mbar_arrive_expect_tx(bar, 2 * kTileBytes);
-        tma_load_4d(smem_u32(sm->k[s]), &tm_k, bar, 0, kv0, g, b);
-        tma_load_4d(smem_u32(sm->v[s]), &tm_v, bar, 0, kv0, g, b);
-        *reinterpret_cast<volatile int*>(&sm->loads_issued) = t + 1;
       }
+      if (!ok) report_abort(a);
     }
     __syncwarp();
   } else if (warp == 8 || warp == 10) {
@@ -304,37 +348,64 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (lane == 0 && x < n_act) {
       const uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, 0, 0);
       const uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, 0, 1);
-      const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[x]));
       const uint32_t tmem_s = tmem + x * 128, tmem_p = tmem + 256 + x * 64, tmem_o = tmem + 384 + x * 64;
       const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
-                     bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]);
-      bool ok = mbar_wait(bar_q, 0, abort_flag);
-      for (int t = -1; ok && t < nt; ++t) {
-        // S of key tile t+1: as soon as the softmax threads have emptied the S columns (copied S of
-        // tile t into registers), so that it is computed underneath their exponentials
-        if (t + 1 < nt) {
-          const int sn = (t + 1) % kFwdStages;
-          if (t >= 0 && !(ok = mbar_wait(bar_se, t & 1, abort_flag))) break;
-          if (!(ok = mbar_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1, abort_flag))) break;
-          tc_fence_after_sync();
-          const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[sn]));
+                     bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]),
+                     bar_of = smem_u32(&sm->bar_o_free[x]);
+      int Ts = 0, Tp = 0;   // key tiles whose S resp. P V have been issued so far
+      bool ok = true;
+
+      // S of key tile t of work item number kq (its Q in buffer kq & 1): as soon as the softmax threads
+      // have emptied the S columns (copied the previous S into registers), so that it is computed
+      // underneath their exponentials
+      auto issue_s = [&](const FwdItem& it, int kq, int t) -> bool {
+        const int qb = kq & 1, s = Ts % kFwdStages;
+        if (t == 0 && !mbar_wait(smem_u32(&sm->bar_q_full[qb]), (kq >> 1) & 1, abort_flag)) return false;
+        if (Ts >= 1 && !mbar_wait(bar_se, (Ts - 1) & 1, abort_flag)) return false;
+        if (!mbar_wait(smem_u32(&sm->bar_kv_full[s]), (Ts / kFwdStages) & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[qb][x]));
+        const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
 #pragma unroll
-          for (int kk = 0; kk < kHeadDim / 16; ++kk)
-            umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
-          umma_commit(bar_s);
-        }
-        // O += P V of key tile t: as soon as P is written
-        if (t >= 0) {
-          if (!(ok = mbar_wait(bar_p, t & 1, abort_flag))) break;
-          tc_fence_after_sync();
-          const int s = t % kFwdStages;
-          const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
+        for (int kk = 0; kk < kHeadDim / 16; ++kk)
+          umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
+        umma_commit(bar_s);
+        if (t == it.nt - 1) umma_commit(smem_u32(&sm->bar_q_empty[qb]));   // Q is free once every tile's S MMAs retire
+        ++Ts;
+        return true;
+      };
+      // O (+)= P V of key tile t of work item number kq: as soon as P is written
+      auto issue_pv = [&](int kq, int t) -> bool {
+        if (!mbar_wait(bar_p, Tp & 1, abort_flag)) return false;
+        // the first P V of an item overwrites O: the previous item's epilogue must have read it
+        if (t == 0 && kq >= 1 && !mbar_wait(bar_of, (kq - 1) & 1, abort_flag)) return false;
+        tc_fence_after_sync();
+        const int s = Tp % kFwdStages;
+        const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
 #pragma unroll
-          for (int kk = 0; kk < kTile / 16; ++kk)
-            umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, t > 0 || kk > 0);
-          umma_commit(bar_o);
-          umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // K[s], V[s] are free once every tile's MMAs on them retire
+        for (int kk = 0; kk < kTile / 16; ++kk)
+          umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, t > 0 || kk > 0);
+        umma_commit(bar_o);
+        umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // K[s], V[s] are free once every tile's MMAs on them retire
+        ++Tp;
+        return true;
+      };
+
+      FwdItem cur, nxt;
+      int k = 0;
+      bool have = fwd_next_item(a, k, n_items, n_act, cur);
+      if (have) ok = issue_s(cur, 0, 0);
+      for (int kq = 0; ok && have; ++kq) {
+        int k_n = k + 1;
+        const bool have_n = fwd_next_item(a, k_n, n_items, n_act, nxt);
+        for (int t = 0; ok && t < cur.nt; ++t) {
+          if (t + 1 < cur.nt) ok = issue_s(cur, kq, t + 1);
+          else if (have_n) ok = issue_s(nxt, kq + 1, 0);   // the next item's first S goes ahead of this item's last P V
+          if (ok) ok = issue_pv(kq, t);
         }
+        cur = nxt;
+        k = k_n;
+        have = have_n;
       }
       if (!ok) report_abort(a);
     }
@@ -342,52 +413,68 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   } else {
   setmaxnreg_inc_216_fwd();
-  if (warp < 4 * n_act) {
+  {
     // -------------------------------------- softmax --------------------------------------
     const int x = warp >> 2;                                      // tile A or B
-    const int h = h0 + x;
     const int r = tid & 127;
-    const int i = q0 + r;                                         // this thread's query position
     const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;   // this warp's TMEM lane quarter
     const uint32_t tmem_s_row = tmem + x * 128 + lane_addr;
     const uint32_t tmem_p_row = tmem + 256 + x * 64 + lane_addr;
     const uint32_t tmem_o_row = tmem + 384 + x * 64 + lane_addr;
     const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
-                   bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]);
-    const float sink2 = a.sinks[h] * kLog2e;
-    FwdRowState st{sink2, 0.f};   // the reference maximum starts at the sink logit
+                   bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]),
+                   bar_of = smem_u32(&sm->bar_o_free[x]);
     const uint32_t bar_exp_mine = n_act == 2 ? smem_u32(&sm->bar_exp[x]) : 0u;
     const uint32_t bar_exp_other = n_act == 2 ? smem_u32(&sm->bar_exp[x ^ 1]) : 0u;
+    int T = 0;   // key tiles so far
     bool ok = true;
 
-    for (int t = 0; t < nt; ++t) {
-      const int kv0 = (t_first + t) * kTile;
-      const bool need_mask = tile_needs_mask(q0, kv0, a.window, len);
-      if (!(ok = warp_all(mbar_wait(bar_s, t & 1, abort_flag)))) break;
-      tc_fence_after_sync();
-      // tile A goes first: its first wait (parity 1 of a fresh barrier) passes at once
-      const uint32_t exp_parity = (x == 0) ? ((t & 1) ^ 1) : (t & 1);
-      ok = need_mask
-          ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, bar_exp_mine, exp_parity,
-                                   bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag)
-          : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, bar_exp_mine, exp_parity,
-                                    bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag);
+    const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+    for (int k = 0; ok && k < n_rounds; ++k) {
+      const int id = fwd_item_id(k);
+      if (id >= n_items || x >= n_act) continue;
+      const FwdItem it = fwd_item(a, id, n_act);
+      const int h = it.h0 + x;
+      const int i = it.q0 + r;                                    // this thread's query position
+      float* lse_out = a.lse + ((long long)(it.b * a.Hq + h)) * a.S_pad + i;
+      if (it.nt == 0) {  // tile is padding only: define its output, no tensor work
+        if (i < a.S) zero_row(a.o.row(it.b, h, i));
+        *lse_out = 0.f;
+        continue;
+      }
+      const float sink2 = a.sinks[h] * kLog2e;
+      FwdRowState st{sink2, 0.f};   // the reference maximum starts at the sink logit
+
+      for (int t = 0; t < it.nt; ++t, ++T) {
+        const int kv0 = (it.t_first + t) * kTile;
+        const bool need_mask = tile_needs_mask(it.q0, kv0, a.window, it.len);
+        if (!(ok = warp_all(mbar_wait(bar_s, T & 1, abort_flag)))) break;
+        tc_fence_after_sync();
+        // tile A goes first: its first wait (parity 1 of a fresh barrier) passes at once
+        const uint32_t exp_parity = (x == 0) ? ((T & 1) ^ 1) : (T & 1);
+        ok = need_mask
+            ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (T - 1) & 1, bar_exp_mine,
+                                     exp_parity, bar_exp_other, a.scale_log2, i, kv0, a.window, it.len, abort_flag)
+            : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (T - 1) & 1, bar_exp_mine,
+                                      exp_parity, bar_exp_other, a.scale_log2, i, kv0, a.window, it.len, abort_flag);
+        if (!ok) break;
+        tmem_wait_st();
+        tc_fence_before_sync();
+        mbar_arrive(bar_p);
+      }
       if (!ok) break;
-      tmem_wait_st();
-      tc_fence_before_sync();
-      mbar_arrive(bar_p);
-    }
-    if (ok) ok = warp_all(mbar_wait(bar_o, (nt - 1) & 1, abort_flag));
-    if (ok) {
+      if (!(ok = warp_all(mbar_wait(bar_o, (T - 1) & 1, abort_flag)))) break;
       tc_fence_after_sync();
       uint32_t o0[32], o1[32];
       tmem_ld32(tmem_o_row, o0);
       tmem_ld32(tmem_o_row + 32, o1);
       tmem_wait_ld();
+      tc_fence_before_sync();
+      mbar_arrive(bar_of);   // the next item's first P V may overwrite O
       const float z = st.l + fast_exp2(sink2 - st.m);   // the sink joins the denominator only
       const float inv = 1.f / z;
       if (i < a.S) {
-        __nv_bfloat16* dst = a.o.row(b, h, i);
+        __nv_bfloat16* dst = a.o.row(it.b, h, i);
 #pragma unroll
         for (int c = 0; c < 32; c += 8) {
           store_bf16x8(dst + c, pack_bf16(__uint_as_float(o0[c]) * inv, __uint_as_float(o0[c + 1]) * inv),
@@ -400,7 +487,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                        pack_bf16(__uint_as_float(o1[c + 6]) * inv, __uint_as_float(o1[c + 7]) * inv));
         }
       }
-      a.lse[((long long)(b * a.Hq + h)) * a.S_pad + i] = (i < len) ? (st.m + log2f(z)) * kLn2 : 0.f;
+      *lse_out = (i < it.len) ? (st.m + log2f(z)) * kLn2 : 0.f;
     }
   }
   }
@@ -413,8 +500,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   if (sm->abort_flag && tid == 9 * 32) {
     // abandoned: give copies still in flight a bounded chance to land before shared memory goes away
-    const int issued = sm->loads_issued;
-    mbar_wait_drain(bar_q, 0);
+    const int issued = sm->loads_issued, q_issued = sm->q_loads_issued;
+    for (int k = max(0, q_issued - 2); k < q_issued; ++k) mbar_wait_drain(smem_u32(&sm->bar_q_full[k & 1]), (k >> 1) & 1);
     for (int t = max(0, issued - kFwdStages); t < issued; ++t)
       mbar_wait_drain(smem_u32(&sm->bar_kv_full[t % kFwdStages]), (t / kFwdStages) & 1);
   }
