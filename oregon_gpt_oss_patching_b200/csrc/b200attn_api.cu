@@ -13,7 +13,6 @@
 #include "bwd_dq_small_kernel.cuh"
 #include "bwd_preprocess_kernel.cuh"
 #include "fwd_kernel.cuh"
-#include "fwd_small_kernel.cuh"
 #include "umma_selftest.cuh"
 
 namespace {
@@ -191,14 +190,22 @@ int b200attn_fwd(const b200attn_params* p) {
   if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
-  const size_t smem = sizeof(FwdSmem) + 1024;
-  if ((rc = set_smem(attn_fwd_kernel, smem))) return rc;
-  int n_sm = 0;
-  if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
   const int heads_per_item = (a.group % 2 == 0) ? 2 : 1;  // two heads of a KV group share staged K/V tiles
-  const long long n_items = (long long)(a.S_pad / kTile) * p->B * (p->Hq / heads_per_item);
-  // persistent: one CTA per SM walks the work items
-  const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);
+  if (p->window > 0 && p->window <= 2 * kTile) {
+    // short work items (at most three key tiles per query tile): the persistent kernel, one CTA per SM
+    // walking the items, hides the per-item set-up and first-load latency that dominate them
+    const size_t smem = sizeof(FwdSmem) + 1024;
+    if ((rc = set_smem(attn_fwd_persistent_kernel, smem))) return rc;
+    int n_sm = 0;
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
+    const long long n_items = (long long)(a.S_pad / kTile) * p->B * (p->Hq / heads_per_item);
+    const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);
+    attn_fwd_persistent_kernel<<<grid, kFwdThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
+    return launch_status();
+  }
+  const size_t smem = sizeof(FwdOneSmem) + 1024;
+  if ((rc = set_smem(attn_fwd_kernel, smem))) return rc;
+  dim3 grid(a.S_pad / kTile, p->Hq / heads_per_item, p->B);
   attn_fwd_kernel<<<grid, kFwdThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
   return launch_status();
 }

@@ -59,48 +59,73 @@ __device__ __forceinline__ DkvItem dkv_item(int it, int nq, int qt_first, int g,
   return DkvItem{g * group + it / nq, (qt_first + it % nq) * kTile};
 }
 
-// P^T and dS^T (bf16 pairs) of 64 query columns for one key row, from S^T/dP^T in registers.
+// P^T and dS^T (bf16 pairs) of 32 query columns for one key row, from S^T/dP^T in registers.
+// Two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
+// slots, should be what the row waits for -- the MMA-issuing warps live on the slots left over.
+template <bool kSelect>
+__device__ __forceinline__ void dkv_compute_chunk(const uint32_t (&rs)[32], const uint32_t (&rp)[32], const float4* nl4,
+                                                  const float4* de4, float2 scale2, uint32_t bits, uint32_t (&pp)[16],
+                                                  uint32_t (&pd)[16]) {
+  const float2 neg1 = make_float2(-1.f, -1.f);
+  float4 Lq[4], Dq[4];
+#pragma unroll
+  for (int e4 = 0; e4 < 8; ++e4) {
+    // the per-column constants of 16 columns at a time, fetched ahead of the arithmetic that uses them
+    if ((e4 & 3) == 0) {
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        Lq[q] = nl4[e4 + q];
+        Dq[q] = de4[e4 + q];
+      }
+    }
+    const float4 L = Lq[e4 & 3];
+    const float4 D = Dq[e4 & 3];
+    const float2 lv[2] = {make_float2(L.x, L.y), make_float2(L.z, L.w)};
+    const float2 dl[2] = {make_float2(D.x, D.y), make_float2(D.z, D.w)};
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int e = e4 * 4 + u * 2;
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2, lv[u]);
+      float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+      if (kSelect) {  // selects, not branches
+        p.x = (bits >> e) & 1u ? p.x : 0.f;
+        p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
+      }
+      const float2 dp = make_float2(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1]));
+      const float2 ds = __fmul2_rn(p, __ffma2_rn(dl[u], neg1, dp));   // P * (dP - delta)
+      pp[e4 * 2 + u] = pack_bf16(p.x, p.y);
+      pd[e4 * 2 + u] = pack_bf16(ds.x, ds.y);
+    }
+  }
+}
+
+// P^T and dS^T of 64 query columns for one key row.  On partly masked tiles (kMask) every 32-query
+// chunk is classified for the whole warp: visible to all 32 key rows (no masking work), to none
+// (zeros without a single exponential -- half the chunks of a sliding-window layer), or mixed.
 template <bool kMask>
 __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], const float* nlse,
                                             const float* delta, float scale_log2, int i0, int j, int window, int len,
                                             uint32_t (&pp)[2][16], uint32_t (&pd)[2][16]) {
-  // two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
-  // slots, should be what the row waits for -- the MMA-issuing warps live on the slots left over
   const float4* nl4 = reinterpret_cast<const float4*>(nlse);
   const float4* de4 = reinterpret_cast<const float4*>(delta);
-  const float2 scale2 = make_float2(scale_log2, scale_log2), neg1 = make_float2(-1.f, -1.f);
-  float4 Lq[4], Dq[4];
+  const float2 scale2 = make_float2(scale_log2, scale_log2);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    const uint32_t bits = kMask ? visible_queries32(j, i0 + c * 32, window, len) : 0xffffffffu;
+    if (kMask) {
+      const uint32_t bits = visible_queries32(j, i0 + c * 32, window, len);
+      if (__all_sync(0xffffffffu, bits == 0u)) {
 #pragma unroll
-    for (int e4 = 0; e4 < 8; ++e4) {
-      // the per-column constants of 16 columns at a time, fetched ahead of the arithmetic that uses them
-      if ((e4 & 3) == 0) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          Lq[q] = nl4[c * 8 + e4 + q];
-          Dq[q] = de4[c * 8 + e4 + q];
+        for (int k = 0; k < 16; ++k) {
+          pp[c][k] = 0u;
+          pd[c][k] = 0u;
         }
+      } else if (__all_sync(0xffffffffu, bits == 0xffffffffu)) {
+        dkv_compute_chunk<false>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, bits, pp[c], pd[c]);
+      } else {
+        dkv_compute_chunk<true>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, bits, pp[c], pd[c]);
       }
-      const float4 L = Lq[e4 & 3];
-      const float4 D = Dq[e4 & 3];
-      const float2 lv[2] = {make_float2(L.x, L.y), make_float2(L.z, L.w)};
-      const float2 dl[2] = {make_float2(D.x, D.y), make_float2(D.z, D.w)};
-#pragma unroll
-      for (int u = 0; u < 2; ++u) {
-        const int e = e4 * 4 + u * 2;
-        const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[c][e]), __uint_as_float(rs[c][e + 1])), scale2, lv[u]);
-        float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-        if (kMask) {  // selects, not branches
-          p.x = (bits >> e) & 1u ? p.x : 0.f;
-          p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
-        }
-        const float2 dp = make_float2(__uint_as_float(rp[c][e]), __uint_as_float(rp[c][e + 1]));
-        const float2 ds = __fmul2_rn(p, __ffma2_rn(dl[u], neg1, dp));   // P * (dP - delta)
-        pp[c][e4 * 2 + u] = pack_bf16(p.x, p.y);
-        pd[c][e4 * 2 + u] = pack_bf16(ds.x, ds.y);
-      }
+    } else {
+      dkv_compute_chunk<false>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, 0xffffffffu, pp[c], pd[c]);
     }
   }
 }

@@ -52,31 +52,51 @@ struct DqSmem {
   int loads_issued;
 };
 
-// dS (bf16 pairs) of 64 key columns for one query row from S/dP in registers; adds sum_j P*dP to pdp.
+// dS (bf16 pairs) of 32 key columns for one query row from S/dP in registers; adds P*dP to acc.
+// Two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
+// slots, should be what the row waits for -- the MMA-issuing warps live on the slots left over.
+template <bool kSelect>
+__device__ __forceinline__ void dq_compute_chunk(const uint32_t (&rs)[32], const uint32_t (&rp)[32], float2 scale2, float2 nl22,
+                                                 float2 neg_delta2, uint32_t bits, uint32_t (&pk)[16], float2& acc) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2, nl22);
+    float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+    if (kSelect) {  // selects, not branches
+      p.x = (bits >> e) & 1u ? p.x : 0.f;
+      p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
+    }
+    const float2 dp = make_float2(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1]));
+    acc = __ffma2_rn(p, dp, acc);
+    const float2 ds = __fmul2_rn(p, __fadd2_rn(dp, neg_delta2));
+    pk[e >> 1] = pack_bf16(ds.x, ds.y);
+  }
+}
+
+// dS of 64 key columns for one query row; adds sum_j P*dP to pdp.  On partly masked tiles (kMask)
+// every 32-key chunk is classified for the whole warp: visible to all 32 rows (no masking work),
+// to none (dS = 0 without a single exponential -- half the chunks of a sliding-window layer), or mixed.
 template <bool kMask>
 __device__ __forceinline__ void dq_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], float scale_log2,
                                            float nl2, float delta, int i, int j0, int window, int len,
                                            uint32_t (&pk)[2][16], float& pdp) {
-  // two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
-  // slots, should be what the row waits for -- the MMA-issuing warps live on the slots left over
   float2 acc = make_float2(0.f, 0.f);
   const float2 scale2 = make_float2(scale_log2, scale_log2), nl22 = make_float2(nl2, nl2);
   const float2 neg_delta2 = make_float2(-delta, -delta);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    const uint32_t bits = kMask ? visible_keys32(i, j0 + c * 32, window, len) : 0xffffffffu;
+    if (kMask) {
+      const uint32_t bits = visible_keys32(i, j0 + c * 32, window, len);
+      if (__all_sync(0xffffffffu, bits == 0u)) {
 #pragma unroll
-    for (int e = 0; e < 32; e += 2) {
-      const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[c][e]), __uint_as_float(rs[c][e + 1])), scale2, nl22);
-      float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-      if (kMask) {  // selects, not branches
-        p.x = (bits >> e) & 1u ? p.x : 0.f;
-        p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
+        for (int k = 0; k < 16; ++k) pk[c][k] = 0u;
+      } else if (__all_sync(0xffffffffu, bits == 0xffffffffu)) {
+        dq_compute_chunk<false>(rs[c], rp[c], scale2, nl22, neg_delta2, bits, pk[c], acc);
+      } else {
+        dq_compute_chunk<true>(rs[c], rp[c], scale2, nl22, neg_delta2, bits, pk[c], acc);
       }
-      const float2 dp = make_float2(__uint_as_float(rp[c][e]), __uint_as_float(rp[c][e + 1]));
-      acc = __ffma2_rn(p, dp, acc);
-      const float2 ds = __fmul2_rn(p, __fadd2_rn(dp, neg_delta2));
-      pk[c][e >> 1] = pack_bf16(ds.x, ds.y);
+    } else {
+      dq_compute_chunk<false>(rs[c], rp[c], scale2, nl22, neg_delta2, 0xffffffffu, pk[c], acc);
     }
   }
   pdp += acc.x + acc.y;

@@ -10,6 +10,7 @@
 #pragma once
 #include "attn_common.cuh"
 #include "bwd_dkdv_kernel.cuh"  // kBlk, kBlkBytes
+#include "bwd_dq_kernel.cuh"    // dq_compute_chunk
 
 namespace b200attn {
 
@@ -36,22 +37,21 @@ template <bool kMask>
 __device__ __forceinline__ void dqs_compute_half(const uint32_t (&rs)[32], const uint32_t (&rp)[32], float scale_log2,
                                                  float nl2, float delta, int i, int j0, int window, int len,
                                                  uint32_t (&pk)[16], float& pdp) {
+  // The 32-key chunk is classified for the whole warp: visible to all 32 rows (no masking work), to
+  // none (dS = 0 without a single exponential -- half the chunks of a sliding-window layer), or mixed.
   const uint32_t bits = kMask ? visible_keys32(i, j0, window, len) : 0xffffffffu;
-  float acc0 = 0.f, acc1 = 0.f;
+  const float2 scale2 = make_float2(scale_log2, scale_log2), nl22 = make_float2(nl2, nl2);
+  const float2 neg_delta2 = make_float2(-delta, -delta);
+  float2 acc = make_float2(0.f, 0.f);
+  if (kMask && __all_sync(0xffffffffu, bits == 0u)) {
 #pragma unroll
-  for (int e = 0; e < 32; e += 2) {
-    float p0 = fast_exp2(fmaf(__uint_as_float(rs[e]), scale_log2, nl2));
-    float p1 = fast_exp2(fmaf(__uint_as_float(rs[e + 1]), scale_log2, nl2));
-    if (kMask) {  // selects, not branches
-      p0 = (bits >> e) & 1u ? p0 : 0.f;
-      p1 = (bits >> (e + 1)) & 1u ? p1 : 0.f;
-    }
-    const float dp0 = __uint_as_float(rp[e]), dp1 = __uint_as_float(rp[e + 1]);
-    acc0 = fmaf(p0, dp0, acc0);
-    acc1 = fmaf(p1, dp1, acc1);
-    pk[e >> 1] = pack_bf16(p0 * (dp0 - delta), p1 * (dp1 - delta));
+    for (int k = 0; k < 16; ++k) pk[k] = 0u;
+  } else if (!kMask || __all_sync(0xffffffffu, bits == 0xffffffffu)) {
+    dq_compute_chunk<false>(rs, rp, scale2, nl22, neg_delta2, bits, pk, acc);
+  } else {
+    dq_compute_chunk<true>(rs, rp, scale2, nl22, neg_delta2, bits, pk, acc);
   }
-  pdp += acc0 + acc1;
+  pdp += acc.x + acc.y;
 }
 
 __global__ void __launch_bounds__(kDqsThreads, 2)

@@ -36,6 +36,7 @@ constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax A, softmax B, {MMA wa
 constexpr int kFwdTmemCols = 512;
 // tensor-memory columns: S_A [0,128) S_B [128,256) P_A [256,320) P_B [320,384) O_A [384,448) O_B [448,512)
 
+// shared memory of the persistent kernel
 struct FwdSmem {
   alignas(1024) uint8_t q[2][2][kTileBytes];   // [buffer][query tile A/B]: the next work item's Q lands while this one runs
   alignas(1024) uint8_t k[kFwdStages][kTileBytes];
@@ -54,6 +55,24 @@ struct FwdSmem {
   int abort_flag;
   int loads_issued;         // K/V tile loads the loader has issued so far (for the abort drain)
   int q_loads_issued;       // Q loads (work items) issued so far
+};
+
+// shared memory of the one-item-per-CTA kernel
+struct FwdOneSmem {
+  alignas(1024) uint8_t q[2][kTileBytes];
+  alignas(1024) uint8_t k[kFwdStages][kTileBytes];
+  alignas(1024) uint8_t v[kFwdStages][kTileBytes];
+  alignas(8) uint64_t bar_q;
+  uint64_t bar_kv_full[kFwdStages];
+  uint64_t bar_kv_empty[kFwdStages];
+  uint64_t bar_s_full[2];   // S of tile X ready                    (tcgen05.commit)
+  uint64_t bar_s_empty[2];  // S of tile X copied into registers    (128 arrivals)
+  uint64_t bar_p_full[2];   // P of tile X written                  (128 arrivals)
+  uint64_t bar_o_full[2];   // P V of tile X retired: P free, O current (tcgen05.commit)
+  uint64_t bar_exp[2];      // tile X may run its exponentials       (128 arrivals of the other tile)
+  uint32_t tmem_base;
+  int abort_flag;
+  int loads_issued;         // K/V tile loads the loader has issued so far (for the abort drain)
 };
 
 // O_row *= alpha for the 64 output columns of this thread's row, in tensor memory
@@ -90,9 +109,16 @@ __device__ __forceinline__ float fwd_row_max(const uint32_t (&s)[4][32]) {
   return fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
 }
 
-// Visibility mask of one 32-key chunk applied to S in registers (branch-free: bit mask, then selects).
-__device__ __forceinline__ void fwd_mask_chunk(uint32_t (&sc)[32], int i, int j0, int window, int len) {
-  const uint32_t bits = visible_keys32(i, j0, window, len);
+// How a 32-key chunk looks to the 32 rows of this warp: the same answer in every lane, so branches on
+// it are warp-uniform.  On the diagonal and at the window's edge most chunks are either visible to
+// all 32 rows (no masking work) or to none (no exponentials at all: P = 0).
+enum : int { kChunkNone = 0, kChunkAll = 1, kChunkSome = 2 };
+__device__ __forceinline__ int fwd_chunk_kind(uint32_t bits) {
+  if (__all_sync(0xffffffffu, bits == 0u)) return kChunkNone;
+  if (__all_sync(0xffffffffu, bits == 0xffffffffu)) return kChunkAll;
+  return kChunkSome;
+}
+__device__ __forceinline__ void fwd_mask_bits(uint32_t (&sc)[32], uint32_t bits) {
 #pragma unroll
   for (int e = 0; e < 32; ++e) sc[e] = (bits >> e) & 1u ? sc[e] : 0xff800000u;  // -inf
 }
@@ -147,9 +173,14 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
     tmem_wait_ld();
     tc_fence_before_sync();
     mbar_arrive(bar_s_empty);   // the tensor core may overwrite S with the next key tile's scores
+    int kind[4] = {kChunkAll, kChunkAll, kChunkAll, kChunkAll};
     if (kMask) {
 #pragma unroll
-      for (int c = 0; c < 4; ++c) fwd_mask_chunk(s[c], i, kv0 + c * 32, window, len);
+      for (int c = 0; c < 4; ++c) {
+        const uint32_t bits = visible_keys32(i, kv0 + c * 32, window, len);
+        kind[c] = fwd_chunk_kind(bits);
+        if (kind[c] != kChunkAll) fwd_mask_bits(s[c], bits);   // (a chunk nobody sees becomes -inf: out of the maximum)
+      }
     }
     st.m = fmaxf(st.m, fwd_row_max(s) * scale_log2);
     const float2 neg_m2 = make_float2(-st.m, -st.m);
@@ -158,7 +189,12 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
     for (int c = 0; c < 4; ++c) {
       uint32_t pk[16];
       if (c == 2 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);
-      fwd_exp_chunk<false>(s[c], scale2, neg_m2, pk, sum, mx);
+      if (kMask && kind[c] == kChunkNone) {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) pk[k] = 0u;
+      } else {
+        fwd_exp_chunk<false>(s[c], scale2, neg_m2, pk, sum, mx);
+      }
       tmem_st16(tmem_p_row + c * 16, pk);
     }
   } else {
@@ -175,8 +211,18 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
     for (int c = 0; c < 4; ++c) {
       if (c < 3) tmem_ld32(tmem_s_row + (c + 1) * 32, s[c + 1]);   // in flight under this chunk's exponentials
       if (c == 2 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);   // hand over early: covers the wake-up latency
-      if (kMask) fwd_mask_chunk(s[c], i, kv0 + c * 32, window, len);
-      fwd_exp_chunk<true>(s[c], scale2, neg_m2, pk[c], sum, mx);
+      int kind = kChunkAll;
+      if (kMask) {
+        const uint32_t bits = visible_keys32(i, kv0 + c * 32, window, len);
+        kind = fwd_chunk_kind(bits);
+        if (kind == kChunkSome) fwd_mask_bits(s[c], bits);
+      }
+      if (kMask && kind == kChunkNone) {
+#pragma unroll
+        for (int k = 0; k < 16; ++k) pk[c][k] = 0u;
+      } else {
+        fwd_exp_chunk<true>(s[c], scale2, neg_m2, pk[c], sum, mx);
+      }
       if (c < 3) tmem_wait_ld();
       if (c == 2) {
         tc_fence_before_sync();
@@ -211,6 +257,221 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
 
 __device__ __forceinline__ void setmaxnreg_inc_216_fwd() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
 __device__ __forceinline__ void setmaxnreg_dec_72_fwd() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
+
+// One CTA = one work item (long items: the hardware's CTA scheduler balances the SMs, and the
+// constant per-CTA addresses keep the MMA-issuing threads' instruction count lowest).
+__global__ void __launch_bounds__(kFwdThreads, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  FwdOneSmem* sm = reinterpret_cast<FwdOneSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5;
+  const int lane = tid & 31;
+  const int b = blockIdx.z;
+  const int n_act = (a.group % 2 == 0) ? 2 : 1;   // query heads (tiles) handled by this CTA
+  const int h0 = blockIdx.y * n_act;
+  const int g = h0 / a.group;
+  const int qt = gridDim.x - 1 - blockIdx.x;      // long (late) tiles first
+  const int q0 = qt * kTile;
+  const int len = seq_len(a, b);
+
+  if (q0 >= len) {  // tile is padding only: define its output, no tensor work
+    if (tid < n_act * kComputeThreads) {
+      const int x = tid >> 7, r = tid & 127;
+      if (q0 + r < a.S) zero_row(a.o.row(b, h0 + x, q0 + r));
+      a.lse[((long long)(b * a.Hq + h0 + x)) * a.S_pad + q0 + r] = 0.f;
+    }
+    return;
+  }
+
+  const int hi = min(q0 + kTile - 1, len - 1);              // last visible key
+  const int lo = a.window ? max(0, q0 - a.window + 1) : 0;  // first visible key
+  const int t_first = lo / kTile;
+  const int nt = hi / kTile - t_first + 1;
+
+  const uint32_t bar_q = smem_u32(&sm->bar_q);
+  volatile int* abort_flag = &sm->abort_flag;
+
+  if (tid == 0) {
+    mbar_init(bar_q, 1);
+    for (int s = 0; s < kFwdStages; ++s) {
+      mbar_init(smem_u32(&sm->bar_kv_full[s]), 1);
+      mbar_init(smem_u32(&sm->bar_kv_empty[s]), n_act);   // one tcgen05.commit per active query tile
+    }
+    for (int x = 0; x < 2; ++x) {
+      mbar_init(smem_u32(&sm->bar_s_full[x]), 1);
+      mbar_init(smem_u32(&sm->bar_s_empty[x]), kComputeThreads);
+      mbar_init(smem_u32(&sm->bar_p_full[x]), kComputeThreads);
+      mbar_init(smem_u32(&sm->bar_o_full[x]), 1);
+      mbar_init(smem_u32(&sm->bar_exp[x]), kComputeThreads);
+    }
+    sm->abort_flag = 0;
+    sm->loads_issued = 0;
+    fence_mbar_init();
+  }
+  if (warp == 8) {
+    __syncwarp();
+    tmem_alloc(smem_u32(&sm->tmem_base), kFwdTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = sm->tmem_base;
+
+  if (warp >= 8) {
+  setmaxnreg_dec_72_fwd();
+
+  if (warp == 9) {
+    // ------------------------------------ TMA loader ------------------------------------
+    if (lane == 0) {
+      prefetch_tmap(&tm_q);
+      prefetch_tmap(&tm_k);
+      prefetch_tmap(&tm_v);
+      mbar_arrive_expect_tx(bar_q, n_act * kTileBytes);
+      for (int x = 0; x < n_act; ++x) tma_load_4d(smem_u32(sm->q[x]), &tm_q, bar_q, 0, q0, h0 + x, b);
+      for (int t = 0; t < nt; ++t) {
+        const int s = t % kFwdStages;
+        if (t >= kFwdStages && !mbar_wait(smem_u32(&sm->bar_kv_empty[s]), ((t / kFwdStages) - 1) & 1, abort_flag)) {
+          report_abort(a);
+          break;
+        }
+        const int kv0 = (t_first + t) * kTile;
+        const uint32_t bar = smem_u32(&sm->bar_kv_full[s]);
+        mbar_arrive_expect_tx(bar, 2 * kTileBytes);
+        tma_load_4d(smem_u32(sm->k[s]), &tm_k, bar, 0, kv0, g, b);
+        tma_load_4d(smem_u32(sm->v[s]), &tm_v, bar, 0, kv0, g, b);
+        *reinterpret_cast<volatile int*>(&sm->loads_issued) = t + 1;
+      }
+    }
+    __syncwarp();
+  } else if (warp == 8 || warp == 10) {
+    // ----------------------- MMA issuer of tile A (warp 8) / tile B (warp 10) -----------------------
+    // One issuing thread per query tile, on different SM sub-partitions: tcgen05.mma issue is
+    // synchronous with the tensor pipe and an issuing warp gets few issue slots next to busy softmax
+    // warps, so one thread for both tiles would serialise the two tiles' chains.
+    const int x = (warp - 8) >> 1;
+    if (lane == 0 && x < n_act) {
+      const uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, 0, 0);
+      const uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, 0, 1);
+      const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[x]));
+      const uint32_t tmem_s = tmem + x * 128, tmem_p = tmem + 256 + x * 64, tmem_o = tmem + 384 + x * 64;
+      const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
+                     bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]);
+      bool ok = mbar_wait(bar_q, 0, abort_flag);
+      for (int t = -1; ok && t < nt; ++t) {
+        // S of key tile t+1: as soon as the softmax threads have emptied the S columns (copied S of
+        // tile t into registers), so that it is computed underneath their exponentials
+        if (t + 1 < nt) {
+          const int sn = (t + 1) % kFwdStages;
+          if (t >= 0 && !(ok = mbar_wait(bar_se, t & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(smem_u32(&sm->bar_kv_full[sn]), ((t + 1) / kFwdStages) & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[sn]));
+#pragma unroll
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)
+            umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
+          umma_commit(bar_s);
+        }
+        // O += P V of key tile t: as soon as P is written
+        if (t >= 0) {
+          if (!(ok = mbar_wait(bar_p, t & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const int s = t % kFwdStages;
+          const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, t > 0 || kk > 0);
+          umma_commit(bar_o);
+          umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // K[s], V[s] are free once every tile's MMAs on them retire
+        }
+      }
+      if (!ok) report_abort(a);
+    }
+    __syncwarp();
+  }
+  } else {
+  setmaxnreg_inc_216_fwd();
+  if (warp < 4 * n_act) {
+    // -------------------------------------- softmax --------------------------------------
+    const int x = warp >> 2;                                      // tile A or B
+    const int h = h0 + x;
+    const int r = tid & 127;
+    const int i = q0 + r;                                         // this thread's query position
+    const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;   // this warp's TMEM lane quarter
+    const uint32_t tmem_s_row = tmem + x * 128 + lane_addr;
+    const uint32_t tmem_p_row = tmem + 256 + x * 64 + lane_addr;
+    const uint32_t tmem_o_row = tmem + 384 + x * 64 + lane_addr;
+    const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
+                   bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]);
+    const float sink2 = a.sinks[h] * kLog2e;
+    FwdRowState st{sink2, 0.f};   // the reference maximum starts at the sink logit
+    const uint32_t bar_exp_mine = n_act == 2 ? smem_u32(&sm->bar_exp[x]) : 0u;
+    const uint32_t bar_exp_other = n_act == 2 ? smem_u32(&sm->bar_exp[x ^ 1]) : 0u;
+    bool ok = true;
+
+    for (int t = 0; t < nt; ++t) {
+      const int kv0 = (t_first + t) * kTile;
+      const bool need_mask = tile_needs_mask(q0, kv0, a.window, len);
+      if (!(ok = warp_all(mbar_wait(bar_s, t & 1, abort_flag)))) break;
+      tc_fence_after_sync();
+      // tile A goes first: its first wait (parity 1 of a fresh barrier) passes at once
+      const uint32_t exp_parity = (x == 0) ? ((t & 1) ^ 1) : (t & 1);
+      ok = need_mask
+          ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (t - 1) & 1, bar_exp_mine, exp_parity,
+                                   bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag)
+          : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (t - 1) & 1, bar_exp_mine, exp_parity,
+                                    bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag);
+      if (!ok) break;
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(bar_p);
+    }
+    if (ok) ok = warp_all(mbar_wait(bar_o, (nt - 1) & 1, abort_flag));
+    if (ok) {
+      tc_fence_after_sync();
+      uint32_t o0[32], o1[32];
+      tmem_ld32(tmem_o_row, o0);
+      tmem_ld32(tmem_o_row + 32, o1);
+      tmem_wait_ld();
+      const float z = st.l + fast_exp2(sink2 - st.m);   // the sink joins the denominator only
+      const float inv = 1.f / z;
+      if (i < a.S) {
+        __nv_bfloat16* dst = a.o.row(b, h, i);
+#pragma unroll
+        for (int c = 0; c < 32; c += 8) {
+          store_bf16x8(dst + c, pack_bf16(__uint_as_float(o0[c]) * inv, __uint_as_float(o0[c + 1]) * inv),
+                       pack_bf16(__uint_as_float(o0[c + 2]) * inv, __uint_as_float(o0[c + 3]) * inv),
+                       pack_bf16(__uint_as_float(o0[c + 4]) * inv, __uint_as_float(o0[c + 5]) * inv),
+                       pack_bf16(__uint_as_float(o0[c + 6]) * inv, __uint_as_float(o0[c + 7]) * inv));
+          store_bf16x8(dst + 32 + c, pack_bf16(__uint_as_float(o1[c]) * inv, __uint_as_float(o1[c + 1]) * inv),
+                       pack_bf16(__uint_as_float(o1[c + 2]) * inv, __uint_as_float(o1[c + 3]) * inv),
+                       pack_bf16(__uint_as_float(o1[c + 4]) * inv, __uint_as_float(o1[c + 5]) * inv),
+                       pack_bf16(__uint_as_float(o1[c + 6]) * inv, __uint_as_float(o1[c + 7]) * inv));
+        }
+      }
+      a.lse[((long long)(b * a.Hq + h)) * a.S_pad + i] = (i < len) ? (st.m + log2f(z)) * kLn2 : 0.f;
+    }
+  }
+  }
+
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 8) {
+    __syncwarp();
+    tmem_dealloc(tmem, kFwdTmemCols);
+  }
+  if (sm->abort_flag && tid == 9 * 32) {
+    // abandoned: give copies still in flight a bounded chance to land before shared memory goes away
+    const int issued = sm->loads_issued;
+    mbar_wait_drain(bar_q, 0);
+    for (int t = max(0, issued - kFwdStages); t < issued; ++t)
+      mbar_wait_drain(smem_u32(&sm->bar_kv_full[t % kFwdStages]), (t / kFwdStages) & 1);
+  }
+}
+
 
 // One unit of work: one 128-row query tile of n_act (1 or 2) query heads of one KV group.
 struct FwdItem {
@@ -261,7 +522,7 @@ __device__ __forceinline__ bool fwd_next_item(const KernelArgs& a, int& k, int n
 // issued before P V of the previous item's last one, so the per-item set-up and first-load latency
 // that dominate short (sliding-window) items are hidden behind the previous item's work.
 __global__ void __launch_bounds__(kFwdThreads, 1)
-attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const KernelArgs a) {
   extern __shared__ uint8_t smem_raw[];
   FwdSmem* sm = reinterpret_cast<FwdSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -352,60 +613,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
                      bar_p = smem_u32(&sm->bar_p_full[x]), bar_o = smem_u32(&sm->bar_o_full[x]),
                      bar_of = smem_u32(&sm->bar_o_free[x]);
-      int Ts = 0, Tp = 0;   // key tiles whose S resp. P V have been issued so far
+      // Two cursors walk the same sequence of (work item, key tile): one for the S MMAs, one, a key
+      // tile behind, for the P V MMAs.  Order of issue: S(first); then S(next), P V(this), S(next), ...
+      // so that S of a key tile -- of the next work item, at an item's end -- is computed underneath the
+      // exponentials of the tile before it.  (Plain locals, no helper closures: this thread gets few
+      // issue slots and every extra instruction lengthens the chains that wait for it.)
+      FwdItem it_s, it_p;
+      int k_s = 0, k_p = 0;      // round of the cursor's work item
+      int kq_s = 0, kq_p = 0;    // work items with key tiles before the cursor's (Q buffer = kq & 1)
+      int t_s = 0, t_p = 0;      // key tile within the work item
+      int Ts = 0, Tp = 0;        // key tiles issued so far (K/V stage = T % kFwdStages)
+      bool have_s = fwd_next_item(a, k_s, n_items, n_act, it_s);
+      bool have_p = have_s;
+      it_p = it_s;
+      k_p = k_s;
       bool ok = true;
-
-      // S of key tile t of work item number kq (its Q in buffer kq & 1): as soon as the softmax threads
-      // have emptied the S columns (copied the previous S into registers), so that it is computed
-      // underneath their exponentials
-      auto issue_s = [&](const FwdItem& it, int kq, int t) -> bool {
-        const int qb = kq & 1, s = Ts % kFwdStages;
-        if (t == 0 && !mbar_wait(smem_u32(&sm->bar_q_full[qb]), (kq >> 1) & 1, abort_flag)) return false;
-        if (Ts >= 1 && !mbar_wait(bar_se, (Ts - 1) & 1, abort_flag)) return false;
-        if (!mbar_wait(smem_u32(&sm->bar_kv_full[s]), (Ts / kFwdStages) & 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[qb][x]));
-        const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
+      bool first = true;
+      while (ok && have_p) {
+        if (have_s) {
+          // S of key tile t_s: Q landed (first tile), the softmax threads have emptied the S columns
+          // (copied the previous S into registers), K landed
+          const int qb = kq_s & 1, s = Ts % kFwdStages;
+          if (t_s == 0 && !(ok = mbar_wait(smem_u32(&sm->bar_q_full[qb]), (kq_s >> 1) & 1, abort_flag))) break;
+          if (Ts >= 1 && !(ok = mbar_wait(bar_se, (Ts - 1) & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(smem_u32(&sm->bar_kv_full[s]), (Ts / kFwdStages) & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[qb][x]));
+          const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]));
 #pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
-        umma_commit(bar_s);
-        if (t == it.nt - 1) umma_commit(smem_u32(&sm->bar_q_empty[qb]));   // Q is free once every tile's S MMAs retire
-        ++Ts;
-        return true;
-      };
-      // O (+)= P V of key tile t of work item number kq: as soon as P is written
-      auto issue_pv = [&](int kq, int t) -> bool {
-        if (!mbar_wait(bar_p, Tp & 1, abort_flag)) return false;
-        // the first P V of an item overwrites O: the previous item's epilogue must have read it
-        if (t == 0 && kq >= 1 && !mbar_wait(bar_of, (kq - 1) & 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const int s = Tp % kFwdStages;
-        const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, t > 0 || kk > 0);
-        umma_commit(bar_o);
-        umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // K[s], V[s] are free once every tile's MMAs on them retire
-        ++Tp;
-        return true;
-      };
-
-      FwdItem cur, nxt;
-      int k = 0;
-      bool have = fwd_next_item(a, k, n_items, n_act, cur);
-      if (have) ok = issue_s(cur, 0, 0);
-      for (int kq = 0; ok && have; ++kq) {
-        int k_n = k + 1;
-        const bool have_n = fwd_next_item(a, k_n, n_items, n_act, nxt);
-        for (int t = 0; ok && t < cur.nt; ++t) {
-          if (t + 1 < cur.nt) ok = issue_s(cur, kq, t + 1);
-          else if (have_n) ok = issue_s(nxt, kq + 1, 0);   // the next item's first S goes ahead of this item's last P V
-          if (ok) ok = issue_pv(kq, t);
+          for (int kk = 0; kk < kHeadDim / 16; ++kk)
+            umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
+          umma_commit(bar_s);
+          ++Ts;
+          if (++t_s == it_s.nt) {
+            umma_commit(smem_u32(&sm->bar_q_empty[qb]));   // Q is free once every tile's S MMAs retire
+            t_s = 0;
+            ++kq_s;
+            ++k_s;
+            have_s = fwd_next_item(a, k_s, n_items, n_act, it_s);
+          }
         }
-        cur = nxt;
-        k = k_n;
-        have = have_n;
+        if (first) {   // the very first S has no P V to go with
+          first = false;
+          continue;
+        }
+        {
+          // O (+)= P V of key tile t_p: P written; the first P V of an item overwrites O, so the previous
+          // item's epilogue must have read it
+          if (!(ok = mbar_wait(bar_p, Tp & 1, abort_flag))) break;
+          if (t_p == 0 && kq_p >= 1 && !(ok = mbar_wait(bar_of, (kq_p - 1) & 1, abort_flag))) break;
+          tc_fence_after_sync();
+          const int s = Tp % kFwdStages;
+          const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]));
+#pragma unroll
+          for (int kk = 0; kk < kTile / 16; ++kk)
+            umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, t_p > 0 || kk > 0);
+          umma_commit(bar_o);
+          umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // K[s], V[s] are free once every tile's MMAs on them retire
+          ++Tp;
+          if (++t_p == it_p.nt) {
+            t_p = 0;
+            ++kq_p;
+            ++k_p;
+            have_p = fwd_next_item(a, k_p, n_items, n_act, it_p);
+          }
+        }
       }
       if (!ok) report_abort(a);
     }
@@ -434,6 +706,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int id = fwd_item_id(k);
       if (id >= n_items || x >= n_act) continue;
       const FwdItem it = fwd_item(a, id, n_act);
+      const float sink = a.sinks[it.h0 + x];
       const int h = it.h0 + x;
       const int i = it.q0 + r;                                    // this thread's query position
       float* lse_out = a.lse + ((long long)(it.b * a.Hq + h)) * a.S_pad + i;
@@ -442,7 +715,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         *lse_out = 0.f;
         continue;
       }
-      const float sink2 = a.sinks[h] * kLog2e;
+      const float sink2 = sink * kLog2e;
       FwdRowState st{sink2, 0.f};   // the reference maximum starts at the sink logit
 
       for (int t = 0; t < it.nt; ++t, ++T) {
