@@ -109,4 +109,22 @@ __device__ __forceinline__ void zero_row(__nv_bfloat16* dst) {
   for (int c = 0; c < kHeadDim; c += 8) store_bf16x8(dst + c, 0u, 0u, 0u, 0u);
 }
 
+// Division by a number fixed for the kernel's life without the hardware's division sequence, whose
+// reciprocal and conversion steps run on the special-function unit and queue up behind the
+// exponentials: quotient estimate by a multiply-high with floor((2^32-1)/d), at most one too small.
+struct FastDiv {
+  uint32_t d, m;
+};
+__device__ __forceinline__ FastDiv make_fastdiv(uint32_t d) { return FastDiv{d, 0xffffffffu / d}; }
+__device__ __forceinline__ void fast_divmod(uint32_t n, const FastDiv& f, int& q, int& r) {
+  uint32_t qq = __umulhi(n, f.m);
+  uint32_t rr = n - qq * f.d;
+  if (rr >= f.d) {
+    ++qq;
+    rr -= f.d;
+  }
+  q = (int)qq;
+  r = (int)rr;
+}
+
 }  // namespace b200attn

@@ -477,14 +477,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 struct FwdItem {
   int b, h0, g, q0, len, t_first, nt;   // nt = visible key tiles; 0 = the tile is padding only
 };
-__device__ __forceinline__ FwdItem fwd_item(const KernelArgs& a, int id, int n_act) {
-  const int n_hp = a.Hq / n_act, n_qt = a.S_pad / kTile, per_qt = a.B * n_hp;
-  const int qt = n_qt - 1 - id / per_qt;   // long (late) query tiles first; neighbouring ids share K/V in L2
-  const int rem = id % per_qt;
+// the divisors of the item decode, prepared once per thread
+struct FwdItemDivs {
+  FastDiv per_qt, n_hp, group;
+  int n_act;
+};
+__device__ __forceinline__ FwdItemDivs fwd_item_divs(const KernelArgs& a, int n_act) {
+  const int n_hp = a.Hq / n_act;
+  return FwdItemDivs{make_fastdiv(a.B * n_hp), make_fastdiv(n_hp), make_fastdiv(a.group), n_act};
+}
+__device__ __forceinline__ FwdItem fwd_item(const KernelArgs& a, int id, const FwdItemDivs& dv) {
+  int q_idx, rem, hp;
   FwdItem it;
-  it.b = rem / n_hp;
-  it.h0 = (rem % n_hp) * n_act;
-  it.g = it.h0 / a.group;
+  fast_divmod(id, dv.per_qt, q_idx, rem);
+  const int qt = a.S_pad / kTile - 1 - q_idx;   // long (late) query tiles first; neighbouring ids share K/V in L2
+  fast_divmod(rem, dv.n_hp, it.b, hp);
+  it.h0 = hp * dv.n_act;
+  int g_rem;
+  fast_divmod(it.h0, dv.group, it.g, g_rem);
   it.q0 = qt * kTile;
   it.len = seq_len(a, it.b);
   if (it.q0 >= it.len) {
@@ -505,12 +515,11 @@ __device__ __forceinline__ int fwd_item_id(int k) {
   return k * (int)gridDim.x + c;
 }
 // first round at or after `k` whose work item exists and has key tiles; false if none
-__device__ __forceinline__ bool fwd_next_item(const KernelArgs& a, int& k, int n_items, int n_act, FwdItem& it) {
-  const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+__device__ __forceinline__ bool fwd_next_item(const KernelArgs& a, int& k, int n_items, int n_rounds, const FwdItemDivs& dv, FwdItem& it) {
   for (; k < n_rounds; ++k) {
     const int id = fwd_item_id(k);
     if (id >= n_items) continue;
-    it = fwd_item(a, id, n_act);
+    it = fwd_item(a, id, dv);
     if (it.nt > 0) return true;
   }
   return false;
@@ -532,6 +541,8 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
   const int lane = tid & 31;
   const int n_act = (a.group % 2 == 0) ? 2 : 1;   // query heads (tiles) handled per work item
   const int n_items = (a.S_pad / kTile) * a.B * (a.Hq / n_act);
+  const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
+  const FwdItemDivs dv = fwd_item_divs(a, n_act);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
@@ -579,7 +590,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       int T = 0;    // key tiles so far (stage = T % kFwdStages)
       bool ok = true;
       FwdItem it;
-      for (int k = 0; ok && fwd_next_item(a, k, n_items, n_act, it); ++k, ++kq) {
+      for (int k = 0; ok && fwd_next_item(a, k, n_items, n_rounds, dv, it); ++k, ++kq) {
         const int qb = kq & 1;
         if (kq >= 2 && !(ok = mbar_wait(smem_u32(&sm->bar_q_empty[qb]), ((kq >> 1) - 1) & 1, abort_flag))) break;
         const uint32_t bar_q = smem_u32(&sm->bar_q_full[qb]);
@@ -623,7 +634,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
       int kq_s = 0, kq_p = 0;    // work items with key tiles before the cursor's (Q buffer = kq & 1)
       int t_s = 0, t_p = 0;      // key tile within the work item
       int Ts = 0, Tp = 0;        // key tiles issued so far (K/V stage = T % kFwdStages)
-      bool have_s = fwd_next_item(a, k_s, n_items, n_act, it_s);
+      bool have_s = fwd_next_item(a, k_s, n_items, n_rounds, dv, it_s);
       bool have_p = have_s;
       it_p = it_s;
       k_p = k_s;
@@ -650,7 +661,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             t_s = 0;
             ++kq_s;
             ++k_s;
-            have_s = fwd_next_item(a, k_s, n_items, n_act, it_s);
+            have_s = fwd_next_item(a, k_s, n_items, n_rounds, dv, it_s);
           }
         }
         if (first) {   // the very first S has no P V to go with
@@ -675,7 +686,7 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
             t_p = 0;
             ++kq_p;
             ++k_p;
-            have_p = fwd_next_item(a, k_p, n_items, n_act, it_p);
+            have_p = fwd_next_item(a, k_p, n_items, n_rounds, dv, it_p);
           }
         }
       }
@@ -701,11 +712,10 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
     int T = 0;   // key tiles so far
     bool ok = true;
 
-    const int n_rounds = (n_items + (int)gridDim.x - 1) / (int)gridDim.x;
     for (int k = 0; ok && k < n_rounds; ++k) {
       const int id = fwd_item_id(k);
       if (id >= n_items || x >= n_act) continue;
-      const FwdItem it = fwd_item(a, id, n_act);
+      const FwdItem it = fwd_item(a, id, dv);
       const float sink = a.sinks[it.h0 + x];
       const int h = it.h0 + x;
       const int i = it.q0 + r;                                    // this thread's query position
