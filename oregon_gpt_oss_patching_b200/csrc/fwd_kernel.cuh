@@ -153,9 +153,10 @@ __device__ __forceinline__ float fwd_sum4(const float2 (&sum)[4]) {
 // reference raised: the row of O in tensor memory and this tile's P (already bf16) are multiplied
 // by 2^(old - new).  P is stored only after the whole row is done, when P V of the previous key tile
 // has certainly left the P columns, so the softmax threads never stand waiting for the tensor core.  `t` is the
-// key-tile counter of this query tile, `prev_parity` the phase of bar_o that the previous key tile's
+// key-tile counter of this query tile (kClassify: 32-key chunks no row of the warp can see are skipped
+// -- worth it where most tiles are partly masked, i.e. in sliding-window layers), `prev_parity` the phase of bar_o that the previous key tile's
 // P V completes.  Returns false when a bounded wait was abandoned.
-template <bool kMask>
+template <bool kMask, bool kClassify>
 __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_t tmem_s_row, uint32_t tmem_p_row,
                                                  uint32_t tmem_o_row, uint32_t bar_s_empty, uint32_t bar_o,
                                                  uint32_t prev_parity, uint32_t bar_exp_mine, uint32_t exp_parity, uint32_t bar_exp_other,
@@ -178,7 +179,7 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
         const uint32_t bits = visible_keys32(i, kv0 + c * 32, window, len);
-        kind[c] = fwd_chunk_kind(bits);
+        kind[c] = kClassify ? fwd_chunk_kind(bits) : kChunkSome;
         if (kind[c] != kChunkAll) fwd_mask_bits(s[c], bits);   // (a chunk nobody sees becomes -inf: out of the maximum)
       }
     }
@@ -189,7 +190,7 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
     for (int c = 0; c < 4; ++c) {
       uint32_t pk[16];
       if (c == 2 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);
-      if (kMask && kind[c] == kChunkNone) {
+      if (kMask && kClassify && kind[c] == kChunkNone) {
 #pragma unroll
         for (int k = 0; k < 16; ++k) pk[k] = 0u;
       } else {
@@ -214,10 +215,10 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
       int kind = kChunkAll;
       if (kMask) {
         const uint32_t bits = visible_keys32(i, kv0 + c * 32, window, len);
-        kind = fwd_chunk_kind(bits);
+        kind = kClassify ? fwd_chunk_kind(bits) : kChunkSome;
         if (kind == kChunkSome) fwd_mask_bits(s[c], bits);
       }
-      if (kMask && kind == kChunkNone) {
+      if (kMask && kClassify && kind == kChunkNone) {
 #pragma unroll
         for (int k = 0; k < 16; ++k) pk[c][k] = 0u;
       } else {
@@ -420,9 +421,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // tile A goes first: its first wait (parity 1 of a fresh barrier) passes at once
       const uint32_t exp_parity = (x == 0) ? ((t & 1) ^ 1) : (t & 1);
       ok = need_mask
-          ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (t - 1) & 1, bar_exp_mine, exp_parity,
+          ? fwd_softmax_tile<true, false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (t - 1) & 1, bar_exp_mine, exp_parity,
                                    bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag)
-          : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (t - 1) & 1, bar_exp_mine, exp_parity,
+          : fwd_softmax_tile<false, false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (t - 1) & 1, bar_exp_mine, exp_parity,
                                     bar_exp_other, a.scale_log2, i, kv0, a.window, len, abort_flag);
       if (!ok) break;
       tmem_wait_st();
@@ -736,9 +737,9 @@ attn_fwd_persistent_kernel(const __grid_constant__ CUtensorMap tm_q, const __gri
         // tile A goes first: its first wait (parity 1 of a fresh barrier) passes at once
         const uint32_t exp_parity = (x == 0) ? ((T & 1) ^ 1) : (T & 1);
         ok = need_mask
-            ? fwd_softmax_tile<true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (T - 1) & 1, bar_exp_mine,
+            ? fwd_softmax_tile<true, true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (T - 1) & 1, bar_exp_mine,
                                      exp_parity, bar_exp_other, a.scale_log2, i, kv0, a.window, it.len, abort_flag)
-            : fwd_softmax_tile<false>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (T - 1) & 1, bar_exp_mine,
+            : fwd_softmax_tile<false, true>(st, t, tmem_s_row, tmem_p_row, tmem_o_row, bar_se, bar_o, (T - 1) & 1, bar_exp_mine,
                                       exp_parity, bar_exp_other, a.scale_log2, i, kv0, a.window, it.len, abort_flag);
         if (!ok) break;
         tmem_wait_st();
