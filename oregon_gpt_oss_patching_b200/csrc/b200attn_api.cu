@@ -243,9 +243,15 @@ int b200attn_bwd_dkdv(const b200attn_params* p) {
   if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
   const size_t smem = sizeof(DkvSmem) + 1024;
-  if ((rc = set_smem(attn_bwd_dkdv_kernel, smem))) return rc;
   dim3 grid(a.S_pad / kTile, p->Hkv, p->B);
-  attn_bwd_dkdv_kernel<<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+  if (p->window > 0 && p->window <= 2 * kTile) {
+    // narrow window: most tiles are partly masked, skipping the chunks nobody sees pays
+    if ((rc = set_smem(attn_bwd_dkdv_kernel<true>, smem))) return rc;
+    attn_bwd_dkdv_kernel<true><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+  } else {
+    if ((rc = set_smem(attn_bwd_dkdv_kernel<false>, smem))) return rc;
+    attn_bwd_dkdv_kernel<false><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+  }
   return launch_status();
 }
 

@@ -99,10 +99,11 @@ __device__ __forceinline__ void dkv_compute_chunk(const uint32_t (&rs)[32], cons
   }
 }
 
-// P^T and dS^T of 64 query columns for one key row.  On partly masked tiles (kMask) every 32-query
-// chunk is classified for the whole warp: visible to all 32 key rows (no masking work), to none
-// (zeros without a single exponential -- half the chunks of a sliding-window layer), or mixed.
-template <bool kMask>
+// P^T and dS^T of 64 query columns for one key row.  With kClassify, on partly masked tiles (kMask)
+// every 32-query chunk is classified for the whole warp: visible to all 32 key rows (no masking
+// work), to none (zeros without a single exponential -- half the chunks of a sliding-window layer),
+// or mixed; it pays where most tiles are partly masked and costs a little where few are.
+template <bool kMask, bool kClassify>
 __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], const float* nlse,
                                             const float* delta, float scale_log2, int i0, int j, int window, int len,
                                             uint32_t (&pp)[2][16], uint32_t (&pd)[2][16]) {
@@ -111,7 +112,7 @@ __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const u
   const float2 scale2 = make_float2(scale_log2, scale_log2);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    if (kMask) {
+    if (kMask && kClassify) {
       const uint32_t bits = visible_queries32(j, i0 + c * 32, window, len);
       if (__all_sync(0xffffffffu, bits == 0u)) {
 #pragma unroll
@@ -125,7 +126,8 @@ __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const u
         dkv_compute_chunk<true>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, bits, pp[c], pd[c]);
       }
     } else {
-      dkv_compute_chunk<false>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, 0xffffffffu, pp[c], pd[c]);
+      const uint32_t bits = kMask ? visible_queries32(j, i0 + c * 32, window, len) : 0xffffffffu;
+      dkv_compute_chunk<kMask>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, bits, pp[c], pd[c]);
     }
   }
 }
@@ -133,6 +135,7 @@ __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const u
 __device__ __forceinline__ void setmaxnreg_inc_216() { asm volatile("setmaxnreg.inc.sync.aligned.u32 216;"); }
 __device__ __forceinline__ void setmaxnreg_dec_72() { asm volatile("setmaxnreg.dec.sync.aligned.u32 72;"); }
 
+template <bool kClassify>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -307,8 +310,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_before_sync();
       mbar_arrive(bar_s_free);  // S^T/dP^T columns may be overwritten by the next item
       uint32_t pp[2][16], pd[2][16];
-      if (need_mask) dkv_compute<true>(rs, rp, sm->nlse[s] + wg * 64, sm->delta[s] + wg * 64, a.scale_log2, i0, j, a.window, len, pp, pd);
-      else dkv_compute<false>(rs, rp, sm->nlse[s] + wg * 64, sm->delta[s] + wg * 64, a.scale_log2, i0, j, a.window, len, pp, pd);
+      if (need_mask) dkv_compute<true, kClassify>(rs, rp, sm->nlse[s] + wg * 64, sm->delta[s] + wg * 64, a.scale_log2, i0, j, a.window, len, pp, pd);
+      else dkv_compute<false, kClassify>(rs, rp, sm->nlse[s] + wg * 64, sm->delta[s] + wg * 64, a.scale_log2, i0, j, a.window, len, pp, pd);
       // the dV/dK MMAs of the previous item must have left the P^T/dS^T columns
       if (it > 0 && !(ok = warp_all(mbar_wait(bar_p_free, (it - 1) & 1, abort_flag)))) break;
       tc_fence_after_sync();

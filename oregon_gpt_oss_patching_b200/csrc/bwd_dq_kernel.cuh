@@ -73,9 +73,7 @@ __device__ __forceinline__ void dq_compute_chunk(const uint32_t (&rs)[32], const
   }
 }
 
-// dS of 64 key columns for one query row; adds sum_j P*dP to pdp.  On partly masked tiles (kMask)
-// every 32-key chunk is classified for the whole warp: visible to all 32 rows (no masking work),
-// to none (dS = 0 without a single exponential -- half the chunks of a sliding-window layer), or mixed.
+// dS of 64 key columns for one query row; adds sum_j P*dP to pdp.
 template <bool kMask>
 __device__ __forceinline__ void dq_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], float scale_log2,
                                            float nl2, float delta, int i, int j0, int window, int len,
@@ -85,19 +83,8 @@ __device__ __forceinline__ void dq_compute(const uint32_t (&rs)[2][32], const ui
   const float2 neg_delta2 = make_float2(-delta, -delta);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
-    if (kMask) {
-      const uint32_t bits = visible_keys32(i, j0 + c * 32, window, len);
-      if (__all_sync(0xffffffffu, bits == 0u)) {
-#pragma unroll
-        for (int k = 0; k < 16; ++k) pk[c][k] = 0u;
-      } else if (__all_sync(0xffffffffu, bits == 0xffffffffu)) {
-        dq_compute_chunk<false>(rs[c], rp[c], scale2, nl22, neg_delta2, bits, pk[c], acc);
-      } else {
-        dq_compute_chunk<true>(rs[c], rp[c], scale2, nl22, neg_delta2, bits, pk[c], acc);
-      }
-    } else {
-      dq_compute_chunk<false>(rs[c], rp[c], scale2, nl22, neg_delta2, 0xffffffffu, pk[c], acc);
-    }
+    const uint32_t bits = kMask ? visible_keys32(i, j0 + c * 32, window, len) : 0xffffffffu;
+    dq_compute_chunk<kMask>(rs[c], rp[c], scale2, nl22, neg_delta2, bits, pk[c], acc);
   }
   pdp += acc.x + acc.y;
 }
