@@ -359,13 +359,13 @@ def run_b200(args, rank, world, local_rank):
 # profiles/ (workload, kernel) -> bytes; absent = not captured.
 NCU_TRAFFIC_BYTES: dict = {
     # cfg3 launches = 4x the rows of the captured B=1, S=8192, window-128 case (traffic grows with rows)
-    ("cfg3", "fwd"): 4 * (83_966_720 + 30_039_296),
-    ("cfg3", "bwd_dkdv"): 4 * (155_233_792 + 12_281_600),
-    ("cfg3", "bwd_dq"): 4 * (155_229_952 + 42_418_944),
+    ("cfg3", "fwd"): 4 * (83_965_184 + 22_961_408),
+    ("cfg3", "bwd_dkdv"): 4 * (155_238_400 + 12_202_240),
+    ("cfg3", "bwd_dq"): 4 * (155_232_768 + 39_927_552),
     # cfg2 launches = 4x the rows of the captured B=1, S=4096 full-causal case
-    ("cfg2", "fwd"): 4 * (42_004_992 + 1_348_608),
-    ("cfg2", "bwd_dkdv"): 4 * (77_642_752 + 4_818_432),
-    ("cfg2", "bwd_dq"): 4 * (77_641_728 + 10_648_576),
+    ("cfg2", "fwd"): 4 * (42_014_464 + 1_208_576),
+    ("cfg2", "bwd_dkdv"): 4 * (77_865_216 + 4_788_480),
+    ("cfg2", "bwd_dq"): 4 * (77_635_328 + 9_793_536),
 }
 
 
