@@ -34,7 +34,8 @@ namespace b200attn {
 constexpr int kDqStages = 3;
 constexpr int kDqThreads = 384;
 constexpr int kDqTmemCols = 512;
-// tensor-memory columns: S [0,128)  dP [128,256)  dS bf16 [256,320)  Q bf16 [320,352)  dO bf16 [352,384)  dQ [384,448)
+// tensor-memory columns: S [0,128)  dP [128,256)  dS bf16 [256,320) and [448,512) (two buffers)  Q bf16 [320,352)
+//                        dO bf16 [352,384)  dQ [384,448)
 
 struct DqSmem {
   alignas(1024) uint8_t k[kDqStages][kTileBytes];
@@ -44,8 +45,9 @@ struct DqSmem {
   uint64_t bar_in_empty[kDqStages];        // the dQ MMAs reading a stage retired
   uint64_t bar_s_full;                     // S and dP ready                 (tcgen05.commit)
   uint64_t bar_s_free;                     // S and dP are in registers      (256 arrivals)
-  uint64_t bar_p_full;                     // dS written                     (256 arrivals)
-  uint64_t bar_p_free;                     // the dQ MMAs have read dS       (tcgen05.commit)
+  uint64_t bar_p_full[2];                  // a dS buffer written            (256 arrivals); one barrier per buffer,
+                                           // so that the writers can never complete two phases unobserved
+  uint64_t bar_p_free[2];                  // the dQ MMAs have read a dS buffer   (tcgen05.commit)
   uint64_t bar_acc;                        // every MMA retired: dQ final
   uint32_t tmem_base;
   int abort_flag;
@@ -120,8 +122,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   const float* nlse_base = a.delta + (long long)a.B * a.Hq * a.S_pad;  // second half of the delta scratch
 
   const uint32_t bar_q = smem_u32(&sm->bar_q), bar_acc = smem_u32(&sm->bar_acc), bar_s_full = smem_u32(&sm->bar_s_full),
-                 bar_s_free = smem_u32(&sm->bar_s_free), bar_p_full = smem_u32(&sm->bar_p_full),
-                 bar_p_free = smem_u32(&sm->bar_p_free);
+                 bar_s_free = smem_u32(&sm->bar_s_free);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
@@ -132,8 +133,10 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
     }
     mbar_init(bar_s_full, 1);
     mbar_init(bar_s_free, 2 * kComputeThreads);
-    mbar_init(bar_p_full, 2 * kComputeThreads);
-    mbar_init(bar_p_free, 1);
+    for (int q = 0; q < 2; ++q) {
+      mbar_init(smem_u32(&sm->bar_p_full[q]), 2 * kComputeThreads);
+      mbar_init(smem_u32(&sm->bar_p_free[q]), 1);
+    }
     mbar_init(bar_acc, 1);
     sm->abort_flag = 0;
     sm->loads_issued = 0;
@@ -148,7 +151,7 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = sm->tmem_base;
-  const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_ds = tmem + 256, tmem_q = tmem + 320, tmem_do = tmem + 352,
+  const uint32_t tmem_s = tmem, tmem_dp = tmem + 128, tmem_ds = tmem + 256, tmem_ds1 = tmem + 448, tmem_q = tmem + 320, tmem_do = tmem + 352,
                  tmem_dq = tmem + 384;
 
   if (warp >= 8) {
@@ -206,14 +209,14 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
       bool ok = true;
       for (int it = 0; ok && it < n_items; ++it) {
-        if (!(ok = mbar_wait(bar_p_full, it & 1, abort_flag))) break;   // dS of the item has been written
+        if (!(ok = mbar_wait(smem_u32(&sm->bar_p_full[it & 1]), (it >> 1) & 1, abort_flag))) break;   // dS of the item has been written
         tc_fence_after_sync();
         const int s = it % kDqStages;
         const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]));
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem_dq, tmem_ds + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(bar_p_free);                      // dS columns reusable once these retire
+          umma_ts(tmem_dq, ((it & 1) ? tmem_ds1 : tmem_ds) + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_commit(smem_u32(&sm->bar_p_free[it & 1]));   // the dS buffer is reusable once these retire
         umma_commit(smem_u32(&sm->bar_in_empty[s]));  // and so is the K/V stage (its S/dP MMAs retired before dS was written)
         if (it == n_items - 1) umma_commit(bar_acc);
       }
@@ -254,10 +257,13 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       mbar_arrive(bar_q);
     }
 
+    bool s_ready = false;
     for (int it = 0; it < n_items; ++it) {
       const int j0 = (kt_first + it) * kTile + wg * 64;  // first key column of this thread
       const bool need_mask = (j0 + 63 > q0) || (a.window != 0 && j0 <= q0 + kTile - 1 - a.window) || (q0 + kTile > len);
-      if (!(ok = warp_all(mbar_wait(bar_s_full, it & 1, abort_flag)))) break;
+      // (the phase was already tested at the end of the previous item, under its stores: a barrier
+      // test costs ~100 cycles even when the phase is complete)
+      if (!warp_all(s_ready) && !(ok = warp_all(mbar_wait(bar_s_full, it & 1, abort_flag)))) break;
       tc_fence_after_sync();
       uint32_t rs[2][32], rp[2][32];
       tmem_ld32(tmem_s + lane_addr + wg * 64, rs[0]);
@@ -267,17 +273,23 @@ attn_bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_k, const __grid_consta
       tmem_wait_ld();
       tc_fence_before_sync();
       mbar_arrive(bar_s_free);  // S/dP columns may be overwritten by the next item
+      // the dQ MMAs of the item before the previous one have long left this dS buffer: ask now, the
+      // answer arrives under the exponentials
+      const uint32_t bar_pf = smem_u32(&sm->bar_p_free[it & 1]);
+      const bool p_free = it < 2 || mbar_test_wait(bar_pf, ((it >> 1) - 1) & 1);
       uint32_t pk[2][16];
       if (need_mask) dq_compute<true>(rs, rp, a.scale_log2, nl2, delta, i, j0, a.window, len, pk, pdp);
       else dq_compute<false>(rs, rp, a.scale_log2, nl2, delta, i, j0, a.window, len, pk, pdp);
-      // the dQ MMAs of the previous item must have left the dS columns
-      if (it > 0 && !(ok = warp_all(mbar_wait(bar_p_free, (it - 1) & 1, abort_flag)))) break;
+      // the dQ MMAs of the item before the previous one must have left this dS buffer (asked above)
+      if (!warp_all(p_free) && !(ok = warp_all(mbar_wait(bar_pf, ((it >> 1) - 1) & 1, abort_flag)))) break;
       tc_fence_after_sync();
-      tmem_st16(tmem_ds + lane_addr + wg * 32, pk[0]);
-      tmem_st16(tmem_ds + lane_addr + wg * 32 + 16, pk[1]);
+      const uint32_t ds = ((it & 1) ? tmem_ds1 : tmem_ds) + lane_addr + wg * 32;
+      tmem_st16(ds, pk[0]);
+      tmem_st16(ds + 16, pk[1]);
+      s_ready = it + 1 < n_items && mbar_test_wait(bar_s_full, (it + 1) & 1);   // answered under the stores
       tmem_wait_st();
       tc_fence_before_sync();
-      mbar_arrive(bar_p_full);
+      mbar_arrive(smem_u32(&sm->bar_p_full[it & 1]));
     }
 
     if (ok) ok = warp_all(mbar_wait(bar_acc, 0, abort_flag));
