@@ -52,12 +52,6 @@ struct DkvSmem {
 
 constexpr uint32_t kDkvStageBytes = 2 * kTileBytes + 2 * kTile * sizeof(float);
 
-struct DkvItem {  // which (head, query tile) an item works on
-  int h, q0;
-};
-__device__ __forceinline__ DkvItem dkv_item(int it, int nq, int qt_first, int g, int group) {
-  return DkvItem{g * group + it / nq, (qt_first + it % nq) * kTile};
-}
 
 // P^T and dS^T (bf16 pairs) of 32 query columns for one key row, from S^T/dP^T in registers.
 // Two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
@@ -211,21 +205,28 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
       tma_load_4d(smem_u32(sm->k), &tm_k, bar_kv, 0, kv0, g, b);
       tma_load_4d(smem_u32(sm->v), &tm_v, bar_kv, 0, kv0, g, b);
+      // items run over a head's query tiles, then the next head of the group (running counters: the
+      // hardware's division sequence would queue behind the exponentials on the special-function unit)
+      int h = g * a.group, qi = 0;
       for (int it = 0; it < n_items; ++it) {
         const int s = it % kDkvStages;
         if (it >= kDkvStages && !mbar_wait(smem_u32(&sm->bar_in_empty[s]), ((it / kDkvStages) - 1) & 1, abort_flag)) {
           report_abort(a);
           break;
         }
-        const DkvItem item = dkv_item(it, nq, qt_first, g, a.group);
+        const int item_q0 = (qt_first + qi) * kTile;
         const uint32_t bar = smem_u32(&sm->bar_in_full[s]);
-        const long long row_off = ((long long)(b * a.Hq + item.h)) * a.S_pad + item.q0;
+        const long long row_off = ((long long)(b * a.Hq + h)) * a.S_pad + item_q0;
         mbar_arrive_expect_tx(bar, kDkvStageBytes);
-        tma_load_4d(smem_u32(sm->q[s]), &tm_q, bar, 0, item.q0, item.h, b);
-        tma_load_4d(smem_u32(sm->d_o[s]), &tm_do, bar, 0, item.q0, item.h, b);
+        tma_load_4d(smem_u32(sm->q[s]), &tm_q, bar, 0, item_q0, h, b);
+        tma_load_4d(smem_u32(sm->d_o[s]), &tm_do, bar, 0, item_q0, h, b);
         bulk_load_1d(smem_u32(sm->nlse[s]), nlse_base + row_off, kTile * sizeof(float), bar);
         bulk_load_1d(smem_u32(sm->delta[s]), a.delta + row_off, kTile * sizeof(float), bar);
         *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
+        if (++qi == nq) {
+          qi = 0;
+          ++h;
+        }
       }
     }
     __syncwarp();
