@@ -359,13 +359,13 @@ def run_b200(args, rank, world, local_rank):
 # profiles/ (workload, kernel) -> bytes; absent = not captured.
 NCU_TRAFFIC_BYTES: dict = {
     # cfg3 launches = 4x the rows of the captured B=1, S=8192, window-128 case (traffic grows with rows)
-    ("cfg3", "fwd"): 4 * (83_965_184 + 22_961_408),
-    ("cfg3", "bwd_dkdv"): 4 * (155_238_400 + 12_202_240),
-    ("cfg3", "bwd_dq"): 4 * (155_232_768 + 39_927_552),
+    ("cfg3", "fwd"): 4 * (83_988_480 + 23_385_600),
+    ("cfg3", "bwd_dkdv"): 4 * (155_260_672 + 11_830_016),
+    ("cfg3", "bwd_dq"): 4 * (155_233_280 + 41_414_400),
     # cfg2 launches = 4x the rows of the captured B=1, S=4096 full-causal case
-    ("cfg2", "fwd"): 4 * (42_014_464 + 1_208_576),
-    ("cfg2", "bwd_dkdv"): 4 * (77_865_216 + 4_788_480),
-    ("cfg2", "bwd_dq"): 4 * (77_635_328 + 9_793_536),
+    ("cfg2", "fwd"): 4 * (42_014_976 + 1_337_088),
+    ("cfg2", "bwd_dkdv"): 4 * (77_644_544 + 4_945_408),
+    ("cfg2", "bwd_dq"): 4 * (77_664_512 + 10_946_304),
 }
 
 
