@@ -163,7 +163,7 @@ def run_b200(args, rank, world, local_rank):
     # device-resident buffers for the kernel-level timing (direct C-ABI calls, no allocation inside)
     o = torch.empty(B, S, Hq, d, dtype=torch.bfloat16, device=dev)
     lse = torch.empty(B, Hq, S_pad, dtype=torch.float32, device=dev)
-    delta = torch.empty((2,) + tuple(lse.shape), dtype=torch.float32, device=dev)
+    delta = torch.empty((_cabi.DELTA_PLANES,) + tuple(lse.shape), dtype=torch.float32, device=dev)
     dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
     dsinks = torch.empty(Hq, dtype=torch.float32, device=dev)
     status = torch.zeros(1, dtype=torch.int32, device=dev)

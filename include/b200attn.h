@@ -39,6 +39,7 @@ extern "C" {
 
 #define B200ATTN_VERSION 1
 #define B200ATTN_ROW_TILE 128 /* lse/delta rows are padded to a multiple of this */
+#define B200ATTN_DELTA_PLANES 10 /* the delta scratch holds this many fp32-sized values per (b, h, padded row) */
 
 enum {
   B200ATTN_OK = 0,
@@ -54,7 +55,7 @@ enum {
 };
 
 /* Largest B * Hq * b200attn_padded_len(S) that b200attn_bwd_static_scratch accepts. */
-#define B200ATTN_STATIC_MAX_ROWS (1 << 20)
+#define B200ATTN_STATIC_MAX_ROWS (1 << 18)
 
 /* bf16 tensor view (batch, head, position, head_dim); strides in ELEMENTS, head_dim stride 1 */
 typedef struct b200attn_tensor {
@@ -83,7 +84,8 @@ typedef struct b200attn_params {
   /* backward only */
   b200attn_tensor d_o;        /* gradient of o */
   b200attn_tensor dq, dk, dv; /* outputs, fully overwritten (no pre-zeroing needed) */
-  float* delta;               /* (2,B,Hq,S_pad) fp32 scratch: [0] rowsum(dO*O), [1] -lse*log2(e) */
+  float* delta;               /* (B200ATTN_DELTA_PLANES,B,Hq,S_pad) fp32-sized scratch: [0] rowsum(dO*O),
+                                 [1] -lse*log2(e), [2..9] MMA side operands of the dK/dV kernel (bf16) */
   float* dsinks;              /* (Hq) fp32 output, overwritten */
   float* dsinks_partial;      /* fp32 scratch of b200attn_dsinks_scratch_floats() elements */
 } b200attn_params;
@@ -120,7 +122,8 @@ int b200attn_bwd(const b200attn_params* p);
 
 /* Backward stages, exported separately so that each can be timed and tested alone. */
 
-/* delta[0] = rowsum(dO * O), delta[1] = -lse * log2(e).  Replaces `_attn_bwd_precompute_D`
+/* delta[0] = rowsum(dO * O), delta[1] = -lse * log2(e), delta[2..9] = the same two per-row constants
+ * as bf16 MMA operand tiles for the dK/dV kernel.  Replaces `_attn_bwd_precompute_D`
  * (attention_kernel.py:102-120).  Reads o, dO, lse; writes delta. */
 int b200attn_bwd_preprocess(const b200attn_params* p);
 
@@ -147,11 +150,11 @@ int b200attn_bwd_dq(const b200attn_params* p);
  * implicit synchronisation) is not acceptable, and bindings from runtimes that own the
  * allocator and do not let foreign code use it.  For them the two scratch buffers of
  * b200attn_bwd (`delta` and `dsinks_partial`, which are ignored here and may be NULL) live in
- * a fixed array inside the library's device image: about 8.3 MB that every GPU loading the
+ * a fixed array inside the library's device image: about 10.6 MB that every GPU loading the
  * library holds until the process exits.  Inputs and outputs are still the caller's.
  *
  *   - Limit: B * Hq * b200attn_padded_len(S) <= B200ATTN_STATIC_MAX_ROWS (e.g. B=1, Hq=64,
- *     S=16384); anything larger returns B200ATTN_ETOOLARGE without launching.
+ *     S=4096); anything larger returns B200ATTN_ETOOLARGE without launching.
  *   - The first call on each device looks up the array's device address (one
  *     cudaGetSymbolAddress per array, with that device current, under a host mutex); make
  *     that first call outside any stream capture.  No call allocates or frees memory.
@@ -168,6 +171,8 @@ int b200attn_bwd_static_scratch(const b200attn_params* p);
  *   mode 0: A (128 x K) and B (N x K) both K-contiguous in shared memory, K = 64, N = 128
  *   mode 1: A from tensor memory (bf16), B given as (K x N) row-major, i.e. N-contiguous,
  *           K = 128, N = 64
+ *   mode 2: mode 0 plus one more k-step, A[:, :16] * B[:, :16]^T, from unswizzled (rows x 16)
+ *           side operands in shared memory
  * a, b: bf16 row-major matrices as described; d: fp32 (128 x N) row-major.
  */
 int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int32_t* status, int device,

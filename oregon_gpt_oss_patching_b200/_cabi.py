@@ -11,6 +11,8 @@ import threading
 
 from . import build as _build
 
+DELTA_PLANES = 10   # B200ATTN_DELTA_PLANES of include/b200attn.h: fp32-sized values per (b, h, padded row) in the delta scratch
+
 EXPORTS = (
     "b200attn_version", "b200attn_sizeof_params", "b200attn_strerror", "b200attn_padded_len", "b200attn_dsinks_scratch_floats",
     "b200attn_fwd", "b200attn_bwd", "b200attn_bwd_preprocess", "b200attn_bwd_dsinks", "b200attn_bwd_dkdv",

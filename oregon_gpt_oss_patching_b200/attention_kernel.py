@@ -150,7 +150,7 @@ class _attention(torch.autograd.Function):
         dq = torch.empty((B, Hq, S, d), dtype=q.dtype, device=q.device)
         dk = torch.empty((B, k.shape[1], S, d), dtype=k.dtype, device=q.device)
         dv = torch.empty((B, k.shape[1], S, d), dtype=v.dtype, device=q.device)
-        delta = torch.empty((2,) + tuple(lse.shape), dtype=torch.float32, device=q.device)
+        delta = torch.empty((_cabi.DELTA_PLANES,) + tuple(lse.shape), dtype=torch.float32, device=q.device)
         dsinks = torch.empty((Hq,), dtype=torch.float32, device=q.device)
         sinks_f32 = sinks.detach().to(torch.float32).contiguous()
         p = _params(q, k, v, o, lse, sinks_f32, ctx.sm_scale, ctx.window, seqlens)

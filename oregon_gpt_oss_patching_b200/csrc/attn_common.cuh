@@ -90,6 +90,11 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr) {
   return make_smem_desc_sw128(smem_addr, kTileBytes, 1024);
 }
+// A (rows x 16) bf16 side operand, K-contiguous, unswizzled: core matrix (row group rg, 8-column
+// half kc) at byte rg*256 + kc*128, element (r, c) at + (r%8)*16 + (c%8)*2.  One k-step of an MMA.
+constexpr int kSideTileBytes = kTile * 16 * 2;   // 4 KB
+__device__ __forceinline__ uint64_t desc_side(uint32_t smem_addr) { return make_smem_desc_noswizzle(smem_addr, 128, 256); }
+__device__ __forceinline__ uint32_t side_offset(int row, int half) { return (row >> 3) * 256 + half * 128 + (row & 7) * 16; }
 constexpr uint32_t kDescKStepKMajor = 32 >> 4;     // +32 B per K-step, in 16-byte units
 constexpr uint32_t kDescKStepMNMajor = 2048 >> 4;  // +2048 B per K-step
 

@@ -291,9 +291,9 @@ int b200attn_bwd(const b200attn_params* p) {
 
 // ---- backward without caller-provided scratch ------------------------------------------------
 // Fixed device-resident scratch for b200attn_bwd_static_scratch.  Every GPU that loads the
-// library holds these ~8.3 MB until the process exits.
+// library holds these ~10.6 MB until the process exits.
 constexpr int64_t kStaticMaxRows = B200ATTN_STATIC_MAX_ROWS;
-static __device__ __align__(256) float g_static_delta[2 * kStaticMaxRows];           // delta | -lse*log2(e)
+static __device__ __align__(256) float g_static_delta[B200ATTN_DELTA_PLANES * kStaticMaxRows];   // delta | -lse*log2(e) | side tiles
 static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 16];  // 8 partials per 128 rows
 
 namespace {
@@ -336,21 +336,22 @@ int b200attn_bwd_static_scratch(const b200attn_params* p) {
 }
 
 int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int32_t* status, int device, void* stream) {
-  if (a == nullptr || b == nullptr || d == nullptr || (mode != 0 && mode != 1)) return B200ATTN_EINVAL;
+  if (a == nullptr || b == nullptr || d == nullptr || (mode < 0 || mode > 2)) return B200ATTN_EINVAL;
   if (!aligned16(a) || !aligned16(b)) return B200ATTN_EALIGN;
   int rc = check_device(device);
   if (rc) return rc;
   DeviceGuard guard(device);
   if (!guard.ok) return B200ATTN_ECUDA;
   CUtensorMap ta, tb;
-  // mode 0: A is (128 x 64), B is (128 x 64).  mode 1: A is read with plain loads, B is (128 x 64).
+  // modes 0, 2: A is (128 x 64), B is (128 x 64).  mode 1: A is read with plain loads, B is (128 x 64).
   b200attn_tensor tb_view{const_cast<void*>(b), 128 * 64, 128 * 64, 64};
-  b200attn_tensor ta_view{const_cast<void*>(mode == 0 ? a : b), 128 * 64, 128 * 64, 64};
+  b200attn_tensor ta_view{const_cast<void*>(mode != 1 ? a : b), 128 * 64, 128 * 64, 64};
   if ((rc = make_map(&ta, ta_view, 1, 1, 128, kTile))) return rc;
   if ((rc = make_map(&tb, tb_view, 1, 1, 128, kTile))) return rc;
   const size_t smem = sizeof(SelftestSmem) + 1024;
   if ((rc = set_smem(umma_selftest_kernel, smem))) return rc;
-  umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, mode, static_cast<const __nv_bfloat16*>(a), d, status);
+  umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, mode, static_cast<const __nv_bfloat16*>(a),
+                                                                                       static_cast<const __nv_bfloat16*>(b), d, status);
   return launch_status();
 }
 

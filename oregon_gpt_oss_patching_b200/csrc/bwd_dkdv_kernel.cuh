@@ -4,14 +4,19 @@
 // tensor memory while it streams, for each of the G query heads of the group, the 128-row query
 // tiles that can see the key tile.  Per item (one head, one query tile), transposed so that keys
 // are the accumulator rows:
-//     S^T  = K Q^T            dP^T = V dO^T                 (tcgen05, fp32 in TMEM, N = 128)
-//     P^T  = 2^(S^T*scale*log2e - LSE*log2e)    dS^T = P^T * (dP^T - delta)   (1 thread / key)
+//     S'^T = K Q^T - LSE/scale        dP'^T = V dO^T - delta      (tcgen05, fp32 in TMEM, N = 128)
+//     P^T  = 2^(S'^T*scale*log2e)     dS^T = P^T * dP'^T          (1 thread / key)
 //     dV  += P^T dO           dK  += dS^T Q                 (A operand = bf16 in TMEM, N = 64)
-// The epilogue stores dV and dK * scale once.  No atomics: every dK/dV element has one owner
+// The per-query-row constants -LSE/scale and -delta are added by the tensor core: one more k-step
+// whose B operand is a (128 queries x 16) side tile, written by the preprocess kernel, holding each
+// constant as three bf16 terms (24 mantissa bits), and whose A operand is a constant tile of ones in
+// the matching columns.  Taken in the compute step instead they are per-COLUMN constants there and
+// cost every thread 32 shared-memory loads per item -- next to the exponentials the most expensive
+// part of the step.  The epilogue stores dV and dK * scale once.  No atomics: every dK/dV element has one owner
 // and is accumulated in fp32 (the reference adds bf16 partial tiles into global memory with
 // atomics, attention_kernel.py:201-212).
 //
-// Pipeline.  Warp 9 streams Q/dO tiles (+ the LSE and delta rows) through a 3-stage TMA ring.
+// Pipeline.  Warp 9 streams Q/dO tiles (+ the side tile) through a 3-stage TMA ring.
 // Warp 8 issues the S^T/dP^T MMAs and warp 10 the dV/dK MMAs.  The two compute warpgroups split
 // the 128 query columns of an item (warps 0-3: columns 0-63, warps 4-7: columns 64-127), pull
 // their half of S^T/dP^T into registers and release those columns at once, so the tensor core
@@ -35,10 +40,11 @@ struct DkvSmem {
   alignas(1024) uint8_t v[kTileBytes];
   alignas(1024) uint8_t q[kDkvStages][kTileBytes];
   alignas(1024) uint8_t d_o[kDkvStages][kTileBytes];
-  alignas(16) float nlse[kDkvStages][kTile];  // -LSE * log2(e) of the item's query rows
-  alignas(16) float delta[kDkvStages][kTile];
+  alignas(128) uint8_t side[kDkvStages][kSideTileBytes];  // per item: (-LSE/scale, -delta) of its query rows, 3 bf16 terms each
+  alignas(128) uint8_t ones_k[kSideTileBytes];            // ones in the columns of the -LSE/scale terms
+  alignas(128) uint8_t ones_v[kSideTileBytes];            // ones in the columns of the -delta terms
   alignas(8) uint64_t bar_kv;                 // K and V landed
-  uint64_t bar_in_full[kDkvStages];           // Q, dO, nlse, delta of a stage landed
+  uint64_t bar_in_full[kDkvStages];           // Q, dO and the side tile of a stage landed
   uint64_t bar_in_empty[kDkvStages];          // the dV/dK MMAs reading a stage retired
   uint64_t bar_s_full;                        // S^T and dP^T ready                  (tcgen05.commit)
   uint64_t bar_s_free;                        // S^T and dP^T are in registers       (256 arrivals)
@@ -50,46 +56,26 @@ struct DkvSmem {
   int loads_issued;
 };
 
-constexpr uint32_t kDkvStageBytes = 2 * kTileBytes + 2 * kTile * sizeof(float);
+constexpr uint32_t kDkvStageBytes = 2 * kTileBytes + kSideTileBytes;
 
 
 // P^T and dS^T (bf16 pairs) of 32 query columns for one key row, from S^T/dP^T in registers.
 // Two elements per instruction (packed fp32 pairs): the special-function unit, not the issue
 // slots, should be what the row waits for -- the MMA-issuing warps live on the slots left over.
 template <bool kSelect>
-__device__ __forceinline__ void dkv_compute_chunk(const uint32_t (&rs)[32], const uint32_t (&rp)[32], const float4* nl4,
-                                                  const float4* de4, float2 scale2, uint32_t bits, uint32_t (&pp)[16],
-                                                  uint32_t (&pd)[16]) {
-  const float2 neg1 = make_float2(-1.f, -1.f);
-  float4 Lq[4], Dq[4];
+__device__ __forceinline__ void dkv_compute_chunk(const uint32_t (&rs)[32], const uint32_t (&rp)[32], float2 scale2,
+                                                  uint32_t bits, uint32_t (&pp)[16], uint32_t (&pd)[16]) {
 #pragma unroll
-  for (int e4 = 0; e4 < 8; ++e4) {
-    // the per-column constants of 16 columns at a time, fetched ahead of the arithmetic that uses them
-    if ((e4 & 3) == 0) {
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        Lq[q] = nl4[e4 + q];
-        Dq[q] = de4[e4 + q];
-      }
+  for (int e = 0; e < 32; e += 2) {
+    const float2 x = __fmul2_rn(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2);
+    float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+    if (kSelect) {  // selects, not branches
+      p.x = (bits >> e) & 1u ? p.x : 0.f;
+      p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
     }
-    const float4 L = Lq[e4 & 3];
-    const float4 D = Dq[e4 & 3];
-    const float2 lv[2] = {make_float2(L.x, L.y), make_float2(L.z, L.w)};
-    const float2 dl[2] = {make_float2(D.x, D.y), make_float2(D.z, D.w)};
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int e = e4 * 4 + u * 2;
-      const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2, lv[u]);
-      float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-      if (kSelect) {  // selects, not branches
-        p.x = (bits >> e) & 1u ? p.x : 0.f;
-        p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
-      }
-      const float2 dp = make_float2(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1]));
-      const float2 ds = __fmul2_rn(p, __ffma2_rn(dl[u], neg1, dp));   // P * (dP - delta)
-      pp[e4 * 2 + u] = pack_bf16(p.x, p.y);
-      pd[e4 * 2 + u] = pack_bf16(ds.x, ds.y);
-    }
+    const float2 ds = __fmul2_rn(p, make_float2(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1])));   // P * (dP - delta)
+    pp[e >> 1] = pack_bf16(p.x, p.y);
+    pd[e >> 1] = pack_bf16(ds.x, ds.y);
   }
 }
 
@@ -98,11 +84,9 @@ __device__ __forceinline__ void dkv_compute_chunk(const uint32_t (&rs)[32], cons
 // work), to none (zeros without a single exponential -- half the chunks of a sliding-window layer),
 // or mixed; it pays where most tiles are partly masked and costs a little where few are.
 template <bool kMask, bool kClassify>
-__device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], const float* nlse,
-                                            const float* delta, float scale_log2, int i0, int j, int window, int len,
-                                            uint32_t (&pp)[2][16], uint32_t (&pd)[2][16]) {
-  const float4* nl4 = reinterpret_cast<const float4*>(nlse);
-  const float4* de4 = reinterpret_cast<const float4*>(delta);
+__device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], float scale_log2,
+                                            int i0, int j, int window, int len, uint32_t (&pp)[2][16],
+                                            uint32_t (&pd)[2][16]) {
   const float2 scale2 = make_float2(scale_log2, scale_log2);
 #pragma unroll
   for (int c = 0; c < 2; ++c) {
@@ -115,13 +99,13 @@ __device__ __forceinline__ void dkv_compute(const uint32_t (&rs)[2][32], const u
           pd[c][k] = 0u;
         }
       } else if (__all_sync(0xffffffffu, bits == 0xffffffffu)) {
-        dkv_compute_chunk<false>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, bits, pp[c], pd[c]);
+        dkv_compute_chunk<false>(rs[c], rp[c], scale2, bits, pp[c], pd[c]);
       } else {
-        dkv_compute_chunk<true>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, bits, pp[c], pd[c]);
+        dkv_compute_chunk<true>(rs[c], rp[c], scale2, bits, pp[c], pd[c]);
       }
     } else {
       const uint32_t bits = kMask ? visible_queries32(j, i0 + c * 32, window, len) : 0xffffffffu;
-      dkv_compute_chunk<kMask>(rs[c], rp[c], nl4 + c * 8, de4 + c * 8, scale2, bits, pp[c], pd[c]);
+      dkv_compute_chunk<kMask>(rs[c], rp[c], scale2, bits, pp[c], pd[c]);
     }
   }
 }
@@ -159,7 +143,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int qt_first = kt;
   const int nq = i_max / kTile - qt_first + 1;  // query tiles per head
   const int n_items = nq * a.group;
-  const float* nlse_base = a.delta + (long long)a.B * a.Hq * a.S_pad;  // second half of the delta scratch
+  // side tiles of the preprocess kernel: planes 2.. of the delta scratch, 32 bytes per query row
+  const uint8_t* side_base = reinterpret_cast<const uint8_t*>(a.delta + 2ll * a.B * a.Hq * a.S_pad);
 
   const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_acc = smem_u32(&sm->bar_acc), bar_s_full = smem_u32(&sm->bar_s_full),
                  bar_s_free = smem_u32(&sm->bar_s_free), bar_p_full = smem_u32(&sm->bar_p_full),
@@ -180,6 +165,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     sm->abort_flag = 0;
     sm->loads_issued = 0;
     fence_mbar_init();
+  }
+  if (tid < kTile) {
+    // constant A operands of the extra k-step: ones in columns 0-2 resp. 4-6 of row `tid`
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    *reinterpret_cast<uint4*>(sm->ones_k + side_offset(tid, 0)) = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
+    *reinterpret_cast<uint4*>(sm->ones_v + side_offset(tid, 0)) = make_uint4(0u, 0u, 0x3f803f80u, 0x00003f80u);
+    *reinterpret_cast<uint4*>(sm->ones_k + side_offset(tid, 1)) = zero;
+    *reinterpret_cast<uint4*>(sm->ones_v + side_offset(tid, 1)) = zero;
+    fence_proxy_async_smem();   // written with ordinary stores, read by the tensor core
   }
   if (warp == 8) {
     __syncwarp();
@@ -220,8 +214,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_arrive_expect_tx(bar, kDkvStageBytes);
         tma_load_4d(smem_u32(sm->q[s]), &tm_q, bar, 0, item_q0, h, b);
         tma_load_4d(smem_u32(sm->d_o[s]), &tm_do, bar, 0, item_q0, h, b);
-        bulk_load_1d(smem_u32(sm->nlse[s]), nlse_base + row_off, kTile * sizeof(float), bar);
-        bulk_load_1d(smem_u32(sm->delta[s]), a.delta + row_off, kTile * sizeof(float), bar);
+        bulk_load_1d(smem_u32(sm->side[s]), side_base + row_off * 32, kSideTileBytes, bar);
         *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
         if (++qi == nq) {
           qi = 0;
@@ -239,6 +232,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t idesc_front = make_idesc_bf16(kTile, kTile, 0, 0);    // A, B both K-contiguous, N = 128
       const uint64_t k_desc = desc_kmajor(smem_u32(sm->k));
       const uint64_t v_desc = desc_kmajor(smem_u32(sm->v));
+      const uint64_t ones_k_desc = desc_side(smem_u32(sm->ones_k)), ones_v_desc = desc_side(smem_u32(sm->ones_v));
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
       for (int it = 0; ok && it < n_items; ++it) {
         // the stage has landed and the previous item's S^T/dP^T are in registers
@@ -248,12 +242,15 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         tc_fence_after_sync();
         const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[s]));
         const uint64_t do_desc = desc_kmajor(smem_u32(sm->d_o[s]));
+        const uint64_t side_desc = desc_side(smem_u32(sm->side[s]));
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
           umma_ss(tmem_st, k_desc + kk * kDescKStepKMajor, q_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+        umma_ss(tmem_st, ones_k_desc, side_desc, idesc_front, 1);    // - LSE/scale per query column
 #pragma unroll
         for (int kk = 0; kk < kHeadDim / 16; ++kk)
           umma_ss(tmem_dpt, v_desc + kk * kDescKStepKMajor, do_desc + kk * kDescKStepKMajor, idesc_front, kk > 0);
+        umma_ss(tmem_dpt, ones_v_desc, side_desc, idesc_front, 1);   // - delta per query column
         umma_commit(bar_s_full);
       }
       if (!ok) report_abort(a);
@@ -295,11 +292,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
 
     int qi = 0;   // query tile of the item within its head (items run over the head's tiles, then the next head)
     for (int it = 0; it < n_items; ++it, qi = (qi + 1 == nq) ? 0 : qi + 1) {
-      const int s = it % kDkvStages;
       const int i0 = (qt_first + qi) * kTile + wg * 64;  // first query column of this thread
       const bool need_mask = (kv0 + kTile - 1 > i0) || (a.window != 0 && kv0 <= i0 + 63 - a.window) || (i0 + 64 > len);
-      // nlse/delta of this stage are read with plain loads below: observe their barrier directly
-      if (!(ok = warp_all(mbar_wait(smem_u32(&sm->bar_in_full[s]), (it / kDkvStages) & 1, abort_flag)))) break;
       if (!(ok = warp_all(mbar_wait(bar_s_full, it & 1, abort_flag)))) break;
       tc_fence_after_sync();
       uint32_t rs[2][32], rp[2][32];
@@ -311,8 +305,8 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tc_fence_before_sync();
       mbar_arrive(bar_s_free);  // S^T/dP^T columns may be overwritten by the next item
       uint32_t pp[2][16], pd[2][16];
-      if (need_mask) dkv_compute<true, kClassify>(rs, rp, sm->nlse[s] + wg * 64, sm->delta[s] + wg * 64, a.scale_log2, i0, j, a.window, len, pp, pd);
-      else dkv_compute<false, kClassify>(rs, rp, sm->nlse[s] + wg * 64, sm->delta[s] + wg * 64, a.scale_log2, i0, j, a.window, len, pp, pd);
+      if (need_mask) dkv_compute<true, kClassify>(rs, rp, a.scale_log2, i0, j, a.window, len, pp, pd);
+      else dkv_compute<false, kClassify>(rs, rp, a.scale_log2, i0, j, a.window, len, pp, pd);
       // the dV/dK MMAs of the previous item must have left the P^T/dS^T columns
       if (it > 0 && !(ok = warp_all(mbar_wait(bar_p_free, (it - 1) & 1, abort_flag)))) break;
       tc_fence_after_sync();

@@ -2,7 +2,10 @@
 //
 // attn_bwd_preprocess_kernel:  delta[b,h,i] = sum_c dO[b,h,i,c] * O[b,h,i,c]  in fp32 (the
 // reference's `_attn_bwd_precompute_D`, attention_kernel.py:102-120); the second half of the
-// scratch receives -LSE*log2(e), the exponent offset the dK/dV and dQ kernels add per query row.
+// scratch receives -LSE*log2(e), the exponent offset the dQ kernels add per query row, and planes
+// 2.. the dK/dV kernel's side tiles: per 128 query rows a (128 x 16) bf16 MMA operand in the
+// unswizzled core-matrix layout (see side_offset) whose row i holds -LSE_i/scale in columns 0-2 and
+// -delta_i in columns 4-6, each as three bf16 terms (hi, mid, lo: 24 mantissa bits), zeros elsewhere.
 //
 // attn_bwd_dsinks_kernel:  dsinks[h] = sum of head h's per-warp partials written by the dQ
 // kernel, in a fixed order with a warp-shuffle tree, so the result is bit-reproducible (the
@@ -26,6 +29,16 @@ __device__ __forceinline__ float dot8_bf16(uint4 x, uint4 y) {
   return s;
 }
 
+// v as three bf16 terms: w0 = (hi, mid), w1 = (lo, 0)
+__device__ __forceinline__ void split_bf16x3(float v, uint32_t& w0, uint32_t& w1) {
+  const __nv_bfloat16 hi = __float2bfloat16_rn(v);
+  const float r1 = v - __bfloat162float(hi);
+  const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+  const __nv_bfloat16 lo = __float2bfloat16_rn(r1 - __bfloat162float(mid));
+  w0 = uint32_t(__bfloat16_as_ushort(hi)) | (uint32_t(__bfloat16_as_ushort(mid)) << 16);
+  w1 = uint32_t(__bfloat16_as_ushort(lo));
+}
+
 // grid (S_pad/128, Hq, B), 128 threads.  Eight lanes share a row (16 bytes of O and of dO
 // each), so a warp covers 4 rows per step and 32 rows in 8 steps.
 __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelArgs a) {
@@ -35,7 +48,13 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
   const int sub = lane >> 3;       // row within the step
   const int part = lane & 7;       // 16-byte slice of the row
   const long long row_base = ((long long)(b * a.Hq + h)) * a.S_pad + (long long)tile * kTile;
-  const long long nlse_off = (long long)a.B * a.Hq * a.S_pad;  // second half of the scratch: -LSE*log2(e)
+  const long long nlse_off = (long long)a.B * a.Hq * a.S_pad;  // plane 1 of the scratch: -LSE*log2(e)
+  uint8_t* side_base = reinterpret_cast<uint8_t*>(a.delta + 2 * nlse_off);   // planes 2..: side tiles, 32 bytes per row
+  const float inv_scale = 1.f / a.scale;
+
+  // the CTA's side tile is put together in shared memory and leaves with coalesced 16-byte stores
+  __shared__ uint4 side_tile[kSideTileBytes / 16];
+  side_tile[side_offset(tid, 1) >> 4] = make_uint4(0u, 0u, 0u, 0u);   // columns 8-15 of row `tid`
 
   uint4 xo[8], xd[8];
 #pragma unroll
@@ -57,10 +76,19 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
     s += __shfl_xor_sync(0xffffffffu, s, 4);
     const int r = warp * 32 + step * 4 + sub;
     if (part == 0) {
+      const float lse = a.lse[row_base + r];
       a.delta[row_base + r] = s;  // zero for padding rows
-      a.delta[nlse_off + row_base + r] = -a.lse[row_base + r] * kLog2e;
+      a.delta[nlse_off + row_base + r] = -lse * kLog2e;
+      uint32_t u0, u1, d0, d1;
+      split_bf16x3(-lse * inv_scale, u0, u1);
+      split_bf16x3(-s, d0, d1);
+      side_tile[side_offset(r, 0) >> 4] = make_uint4(u0, u1, d0, d1);   // r is the row within the tile
     }
   }
+  __syncthreads();
+  uint4* dst = reinterpret_cast<uint4*>(side_base + row_base * 32);   // this CTA's 128 rows
+  dst[tid] = side_tile[tid];
+  dst[tid + 128] = side_tile[tid + 128];
 }
 
 // grid (Hq), 256 threads

@@ -228,6 +228,16 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
          (uint64_t(sbo_bytes >> 4) << 32) | (uint64_t(1) << 46) | (uint64_t(2) << 61);
 }
 
+// Shared-memory descriptor of a K-contiguous operand WITHOUT swizzle: the tile is made of
+// 8-row x 16-byte core matrices (128 contiguous bytes each); `lbo_bytes` is the distance between
+// core matrices that are neighbours along K, `sbo_bytes` between neighbouring 8-row groups.
+// Bits 61-63 = 0 selects the unswizzled layout.  The tile base must be 16-byte aligned.
+__device__ __forceinline__ uint64_t make_smem_desc_noswizzle(uint32_t smem_addr, uint32_t lbo_bytes,
+                                                             uint32_t sbo_bytes) {
+  return uint64_t((smem_addr & 0x3FFFFu) >> 4) | (uint64_t(lbo_bytes >> 4) << 16) |
+         (uint64_t(sbo_bytes >> 4) << 32) | (uint64_t(1) << 46);
+}
+
 // D[tmem] (+)= A[smem] * B[smem]
 __device__ __forceinline__ void umma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                         uint32_t accumulate) {

@@ -4,6 +4,8 @@
 //   mode 0: D(128x128) = A(128x64) * B(128x64)^T     A, B from shared memory, K-contiguous
 //   mode 1: D(128x64)  = A(128x128) * B(128x64)      A bf16 from tensor memory, B from shared
 //                                                     memory read N-contiguous
+//   mode 2: mode 0 plus one more k-step, A[:, :16] * B[:, :16]^T, from unswizzled (rows x 16)
+//           side operands written by the threads (the form the dK/dV kernel's row constants take)
 #pragma once
 #include "attn_common.cuh"
 
@@ -12,6 +14,8 @@ namespace b200attn {
 struct SelftestSmem {
   alignas(1024) uint8_t a[kTileBytes];
   alignas(1024) uint8_t b[kTileBytes];
+  alignas(128) uint8_t a2[kSideTileBytes];
+  alignas(128) uint8_t b2[kSideTileBytes];
   alignas(8) uint64_t bar_load;
   uint64_t bar_mma;
   uint32_t tmem_base;
@@ -20,7 +24,7 @@ struct SelftestSmem {
 
 __global__ void __launch_bounds__(128)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, int mode,
-                     const __nv_bfloat16* a_global, float* d, int* status) {
+                     const __nv_bfloat16* a_global, const __nv_bfloat16* b_global, float* d, int* status) {
   extern __shared__ uint8_t smem_raw[];
   SelftestSmem* sm = reinterpret_cast<SelftestSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -46,7 +50,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   const uint32_t lane_addr = uint32_t(warp * 32) << 16;
 
   if (tid == 0) {
-    if (mode == 0) {
+    if (mode != 1) {
       mbar_arrive_expect_tx(bar_load, 2 * kTileBytes);
       tma_load_4d(smem_u32(sm->a), &tm_a, bar_load, 0, 0, 0, 0);
     } else {
@@ -65,15 +69,26 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     }
     tmem_wait_st();
   }
+  if (mode == 2) {  // thread r puts the first 16 elements of row r of A and of B into the side tiles
+    const uint4* ra = reinterpret_cast<const uint4*>(a_global + tid * 64);
+    const uint4* rb = reinterpret_cast<const uint4*>(b_global + tid * 64);
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      *reinterpret_cast<uint4*>(sm->a2 + side_offset(tid, half)) = ra[half];
+      *reinterpret_cast<uint4*>(sm->b2 + side_offset(tid, half)) = rb[half];
+    }
+    fence_proxy_async_smem();   // written with ordinary stores, read by the tensor core
+  }
   bool ok = warp_all(mbar_wait(bar_load, 0, abort_flag));
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
   if (ok && tid == 0) {
-    if (mode == 0) {
+    if (mode != 1) {
       const uint32_t idesc = make_idesc_bf16(128, 128, 0, 0);
       const uint64_t da = desc_kmajor(smem_u32(sm->a)), db = desc_kmajor(smem_u32(sm->b));
       for (int kk = 0; kk < 4; ++kk) umma_ss(tmem, da + kk * kDescKStepKMajor, db + kk * kDescKStepKMajor, idesc, kk > 0);
+      if (mode == 2) umma_ss(tmem, desc_side(smem_u32(sm->a2)), desc_side(smem_u32(sm->b2)), idesc, 1);
     } else {
       const uint32_t idesc = make_idesc_bf16(128, 64, 0, 1);
       const uint64_t db = desc_mnmajor(smem_u32(sm->b));
@@ -85,7 +100,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   ok = ok && warp_all(mbar_wait(bar_mma, 0, abort_flag));
   if (ok) {
     tc_fence_after_sync();
-    const int n = mode == 0 ? 128 : 64;
+    const int n = mode != 1 ? 128 : 64;
     uint32_t r[32];
     for (int c = 0; c < n / 32; ++c) {
       tmem_ld32(tmem + lane_addr + c * 32, r);

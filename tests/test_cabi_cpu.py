@@ -94,3 +94,10 @@ def test_seqlens_from_mask_forms():
     assert seqlens_from_mask(None, 2, 4) is None
     with pytest.raises(ValueError):
         seqlens_from_mask(torch.zeros(2, 5), 2, 4)
+
+
+def test_delta_planes_constant_matches_the_header():
+    import re
+    from oregon_gpt_oss_patching_b200 import _cabi
+    text = open(os.path.join(os.path.dirname(__file__), "..", "include", "b200attn.h")).read()
+    assert int(re.search(r"#define B200ATTN_DELTA_PLANES (\d+)", text).group(1)) == _cabi.DELTA_PLANES

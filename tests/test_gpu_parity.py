@@ -14,19 +14,21 @@ pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 
 
-@pytest.mark.parametrize("mode", [0, 1])
+@pytest.mark.parametrize("mode", [0, 1, 2])
 def test_umma_building_blocks(mode):
     lib = _cabi.load()
     g = torch.Generator().manual_seed(mode)
-    a = torch.randn(128, 64 if mode == 0 else 128, generator=g).to(torch.bfloat16).to(DEV)
+    a = torch.randn(128, 128 if mode == 1 else 64, generator=g).to(torch.bfloat16).to(DEV)
     b = torch.randn(128, 64, generator=g).to(torch.bfloat16).to(DEV)
-    n = 128 if mode == 0 else 64
+    n = 64 if mode == 1 else 128
     d = torch.full((128, n), float("nan"), device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     rc = lib.b200attn_umma_selftest(mode, a.data_ptr(), b.data_ptr(), d.data_ptr(), status.data_ptr(), 0, None)
     torch.cuda.synchronize()
     assert rc == 0 and status.item() == 0
-    ref = a.float() @ (b.float().t() if mode == 0 else b.float())
+    ref = a.float() @ (b.float() if mode == 1 else b.float().t())
+    if mode == 2:   # one more k-step from unswizzled side operands: the first 16 columns again
+        ref = ref + a.float()[:, :16] @ b.float()[:, :16].t()
     assert rel_err(d, ref) < 1e-5
 
 
@@ -53,7 +55,7 @@ def test_lse_and_delta_stage(name):
     o = torch.empty(B, S, Hq, d, dtype=torch.bfloat16, device=DEV)
     S_pad = _cabi.padded_len(S)
     lse = torch.full((B, Hq, S_pad), float("nan"), device=DEV)
-    delta = torch.full((2, B, Hq, S_pad), float("nan"), device=DEV)
+    delta = torch.full((_cabi.DELTA_PLANES, B, Hq, S_pad), float("nan"), device=DEV)
     status = torch.zeros(1, dtype=torch.int32, device=DEV)
     p = _cabi.Params()
     p.B, p.Hq, p.Hkv, p.S, p.d, p.window, p.scale, p.device = B, Hq, k.shape[1], S, d, g["window"], g["scale"], 0

@@ -53,7 +53,7 @@ def test_static_scratch_backward_matches_the_allocating_one_twice_in_a_row(windo
         lib, p, t = _setup(case, shift)
         # ordinary entry point with caller-owned scratch
         want = _outputs(p, t["q"], t["k"], t["v"], 16)
-        delta = torch.empty(2, 2, 16, _cabi.padded_len(S), device=DEV)
+        delta = torch.empty(_cabi.DELTA_PLANES, 2, 16, _cabi.padded_len(S), device=DEV)
         part = torch.empty(int(lib.b200attn_dsinks_scratch_floats(ctypes.byref(p))), device=DEV)
         p.delta, p.dsinks_partial = delta.data_ptr(), part.data_ptr()
         assert lib.b200attn_bwd(ctypes.byref(p)) == 0
@@ -71,6 +71,6 @@ def test_static_scratch_backward_matches_the_allocating_one_twice_in_a_row(windo
 def test_static_scratch_rejects_problems_beyond_its_limit():
     lib = _cabi.load()
     p = _cabi.Params()
-    p.B, p.Hq, p.Hkv, p.S, p.d, p.scale, p.device = 2, 64, 8, 16384, 64, 0.125, 0   # 2*64*16384 rows > 2^20
+    p.B, p.Hq, p.Hkv, p.S, p.d, p.scale, p.device = 2, 64, 8, 16384, 64, 0.125, 0   # 2*64*16384 rows > 2^18
     assert lib.b200attn_bwd_static_scratch(ctypes.byref(p)) == -9
     assert b"B200ATTN_STATIC_MAX_ROWS" in lib.b200attn_strerror(-9)
