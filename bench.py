@@ -359,13 +359,13 @@ def run_b200(args, rank, world, local_rank):
 # profiles/ (workload, kernel) -> bytes; absent = not captured.
 NCU_TRAFFIC_BYTES: dict = {
     # cfg3 launches = 4x the rows of the captured B=1, S=8192, window-128 case (traffic grows with rows)
-    ("cfg3", "fwd"): 4 * (83_988_480 + 23_385_600),
-    ("cfg3", "bwd_dkdv"): 4 * (155_260_672 + 11_830_016),
-    ("cfg3", "bwd_dq"): 4 * (155_233_280 + 41_414_400),
+    ("cfg3", "fwd"): 4 * (83_964_928 + 25_175_296),
+    ("cfg3", "bwd_dkdv"): 4 * (167_818_240 + 10_284_800),
+    ("cfg3", "bwd_dq"): 4 * (155_234_048 + 39_901_440),
     # cfg2 launches = 4x the rows of the captured B=1, S=4096 full-causal case
-    ("cfg2", "fwd"): 4 * (42_014_976 + 1_337_088),
-    ("cfg2", "bwd_dkdv"): 4 * (77_644_544 + 4_945_408),
-    ("cfg2", "bwd_dq"): 4 * (77_664_512 + 10_946_304),
+    ("cfg2", "fwd"): 4 * (42_022_144 + 2_042_112),
+    ("cfg2", "bwd_dkdv"): 4 * (84_045_568 + 5_633_536),
+    ("cfg2", "bwd_dq"): 4 * (77_636_096 + 10_991_872),
 }
 
 
