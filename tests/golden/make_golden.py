@@ -90,7 +90,7 @@ def run_triton(ref_dir, case, q, k, v, do, sinks):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="checkout of nlp-uoregon/oregon_gpt_oss_patching")
     ap.add_argument("--skip-cfg1-triton", action="store_true")
     args = ap.parse_args()
     torch.manual_seed(0)
