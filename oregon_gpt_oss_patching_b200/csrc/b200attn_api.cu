@@ -10,7 +10,7 @@
 #include "attn_common.cuh"
 #include "bwd_dkdv_kernel.cuh"
 #include "bwd_dq_kernel.cuh"
-#include "bwd_dq_small_kernel.cuh"
+#include "bwd_dq_persistent_kernel.cuh"
 #include "bwd_preprocess_kernel.cuh"
 #include "fwd_kernel.cuh"
 #include "umma_selftest.cuh"
@@ -191,8 +191,8 @@ int b200attn_fwd(const b200attn_params* p) {
   if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
   const int heads_per_item = (a.group % 2 == 0) ? 2 : 1;  // two heads of a KV group share staged K/V tiles
-  if (p->window > 0 && p->window <= 2 * kTile) {
-    // short work items (at most three key tiles per query tile): the persistent kernel, one CTA per SM
+  if (p->window > 0 && p->window <= 32 * kTile) {
+    // short work items (measured cross-over near 4096 keys): the persistent kernel, one CTA per SM
     // walking the items, hides the per-item set-up and first-load latency that dominate them
     const size_t smem = sizeof(FwdSmem) + 1024;
     if ((rc = set_smem(attn_fwd_persistent_kernel, smem))) return rc;
@@ -263,13 +263,21 @@ int b200attn_bwd_dq(const b200attn_params* p) {
   CUtensorMap tk, tv;
   const KernelArgs a = make_args(p);
   dim3 grid(a.S_pad / kTile, p->Hq, p->B);
-  if (p->window > 0 && p->window <= kTile) {
-    // short key range (at most four 64-key blocks per query tile): the half-size kernel, two CTAs per SM
-    if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kBlk))) return rc;
-    if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kBlk))) return rc;
-    const size_t smem = sizeof(DqsSmem) + 1024;
-    if ((rc = set_smem(attn_bwd_dq_small_kernel, smem))) return rc;
-    attn_bwd_dq_small_kernel<<<grid, kDqsThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tk, tv, a);
+  if (p->window > 0 && p->window <= 8 * kTile) {
+    // short work items (at most nine key tiles per query tile; measured cross-over between 1024 and 2048
+    // keys): the persistent kernel, one CTA per SM walking the items
+    CUtensorMap tq, tdo;
+    if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
+    if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
+    if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
+    if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
+    const size_t smem = sizeof(DqpSmem) + 1024;
+    if ((rc = set_smem(attn_bwd_dq_persistent_kernel, smem))) return rc;
+    int n_sm = 0;
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
+    const long long n_items = (long long)(a.S_pad / kTile) * p->B * p->Hq;
+    const unsigned pgrid = (unsigned)(n_items < n_sm ? n_items : n_sm);
+    attn_bwd_dq_persistent_kernel<<<pgrid, kDqpThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tdo, tk, tv, a);
     return launch_status();
   }
   if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;

@@ -28,8 +28,6 @@
 
 namespace b200attn {
 
-constexpr int kBlk = 64;                        // rows of the 64-row blocks the dQ kernel streams
-constexpr int kBlkBytes = kBlk * kHeadDim * 2;  // 8 KB
 constexpr int kDkvStages = 3;
 constexpr int kDkvThreads = 384;
 constexpr int kDkvTmemCols = 512;

@@ -86,9 +86,11 @@ def test_lse_and_delta_stage(name):
 @pytest.mark.parametrize("S,window,Hq,Hkv,B", [
     (64, 0, 8, 1, 1), (1, 0, 2, 1, 1), (127, 0, 2, 2, 2), (129, 128, 8, 1, 1), (255, 64, 4, 2, 1),
     (384, 128, 8, 1, 2), (640, 0, 16, 2, 1), (513, 256, 8, 4, 1), (1000, 128, 8, 1, 1), (300, 1, 2, 1, 1),
-    # windows either side of the switch between the persistent and the one-item-per-CTA forward kernel,
+    # windows either side of the switch of the dK/dV kernel variants (256),
     # an odd group size (one query head per work item), and enough work items for several rounds per CTA
     (1000, 200, 6, 2, 2), (1500, 256, 8, 1, 2), (1500, 257, 8, 2, 1), (20000, 128, 8, 1, 1), (9000, 100, 3, 1, 2),
+    # either side of the dQ (1024) and forward (4096) switches between persistent and one-item kernels
+    (3000, 1024, 8, 2, 1), (3000, 1025, 8, 2, 1), (6000, 4096, 4, 1, 1), (6000, 4097, 4, 1, 1),
 ])
 def test_odd_shapes_vs_oracle(S, window, Hq, Hkv, B):
     case = AttnCase("t", B=B, S=S, Hq=Hq, Hkv=Hkv, window=window, seed=100 + S)
