@@ -359,9 +359,9 @@ def run_b200(args, rank, world, local_rank):
 # profiles/ (workload, kernel) -> bytes; absent = not captured.
 NCU_TRAFFIC_BYTES: dict = {
     # cfg3 launches = 4x the rows of the captured B=1, S=8192, window-128 case (traffic grows with rows)
-    ("cfg3", "fwd"): 4 * (83_964_928 + 25_175_296),
-    ("cfg3", "bwd_dkdv"): 4 * (167_818_240 + 10_284_800),
-    ("cfg3", "bwd_dq"): 4 * (155_234_048 + 39_901_440),
+    ("cfg3", "fwd"): 4 * (83_966_464 + 23_717_632),
+    ("cfg3", "bwd_dkdv"): 4 * (167_820_800 + 11_823_872),
+    ("cfg3", "bwd_dq"): 4 * (155_429_120 + 38_473_216),
     # cfg2 launches = 4x the rows of the captured B=1, S=4096 full-causal case
     ("cfg2", "fwd"): 4 * (42_022_144 + 2_042_112),
     ("cfg2", "bwd_dkdv"): 4 * (84_045_568 + 5_633_536),
