@@ -11,6 +11,13 @@ rank runs the same per-GPU workload on its own (batch x KV-group) units -- atten
 exchange between units, so there is no collective on the data path; only the timing is
 reduced (max over ranks).  One JSON line is printed by rank 0.
 
+At N = 1 the line also carries `triton_reference`: the reference project's own Triton kernel run
+through its stock `attention()` on the same GPU, same seeded inputs and same event protocol
+(imported from `--reference-path`, `$REFERENCE_PATH` or `baseline/_ref`; "unavailable" with the
+reason when it cannot be imported), and `cpu_baseline_cfg1`: the unmodified `transformers`
+eager attention in fp32 on the CPU-runnable configuration.  At N > 1 it carries `strong`: the
+named configurations sharded by KV-head group across the ranks (total work fixed).
+
 `--impl reference` times the reference's CPU path for the same function (fp32 eager attention
 evaluated slice by slice by the oracle port) on the host cores, on a bounded sample.
 """
@@ -133,6 +140,43 @@ def shape_case(shape: str):
     return AttnCase(f"B{B}_S{S}_W{window}", B=B, S=S, window=window)
 
 
+def resident_problem(lib, q, k, v, do, sinks, seqlens, scale, window, device_index, stream):
+    """C-ABI parameter block for device-resident inputs, with every output and scratch buffer allocated.
+
+    q (B,Hq,S,d), k/v (B,Hkv,S,d), do (B,S,Hq,d): bf16 device tensors (any outer strides).  Returns the block
+    and a dict that keeps the buffers alive.
+    """
+    import ctypes
+    from oregon_gpt_oss_patching_b200 import _cabi
+    dev = q.device
+    B, Hq, S, d = q.shape
+    Hkv = k.shape[1]
+    S_pad = _cabi.padded_len(S)
+    keep = {
+        "o": torch.empty(B, S, Hq, d, dtype=torch.bfloat16, device=dev),
+        "lse": torch.empty(B, Hq, S_pad, dtype=torch.float32, device=dev),
+        "delta": torch.empty((_cabi.DELTA_PLANES, B, Hq, S_pad), dtype=torch.float32, device=dev),
+        "dq": torch.empty(B, Hq, S, d, dtype=torch.bfloat16, device=dev),
+        "dk": torch.empty(B, Hkv, S, d, dtype=torch.bfloat16, device=dev),
+        "dv": torch.empty(B, Hkv, S, d, dtype=torch.bfloat16, device=dev),
+        "dsinks": torch.empty(Hq, dtype=torch.float32, device=dev),
+        "status": torch.zeros(1, dtype=torch.int32, device=dev),
+        "sinks_f32": sinks.float().contiguous(),
+        "inputs": (q, k, v, do, seqlens),
+    }
+    p = _cabi.Params()
+    p.B, p.Hq, p.Hkv, p.S, p.d, p.window, p.scale, p.device = B, Hq, Hkv, S, d, window, scale, device_index
+    p.stream, p.status, p.sinks = stream.cuda_stream, keep["status"].data_ptr(), keep["sinks_f32"].data_ptr()
+    p.seqlens = seqlens.data_ptr() if seqlens is not None else None
+    p.q, p.k, p.v = (_cabi.tensor4(t, "bhsd") for t in (q, k, v))
+    p.o, p.d_o = _cabi.tensor4(keep["o"], "bshd"), _cabi.tensor4(do, "bshd")
+    p.lse, p.delta = keep["lse"].data_ptr(), keep["delta"].data_ptr()
+    p.dq, p.dk, p.dv = (_cabi.tensor4(keep[x], "bhsd") for x in ("dq", "dk", "dv"))
+    keep["partial"] = torch.empty(int(lib.b200attn_dsinks_scratch_floats(ctypes.byref(p))), dtype=torch.float32, device=dev)
+    p.dsinks, p.dsinks_partial = keep["dsinks"].data_ptr(), keep["partial"].data_ptr()
+    return p, keep
+
+
 def run_b200(args, rank, world, local_rank):
     from oracle import CONFIGS, algorithmic_bytes, algorithmic_flops, make_inputs
     import ctypes
@@ -153,6 +197,9 @@ def run_b200(args, rank, world, local_rank):
     case_r = dataclasses.replace(case, seed=case.seed + rank)
     q, k, v, do, sinks = make_inputs(case_r, dtype=torch.bfloat16, device="cpu")
     seqlens = None if case.seqlens is None else torch.tensor(case.seqlens, dtype=torch.int32, device=dev)
+    # the pinned staging buffers of the end-to-end leg are first touched by a thread bound to the GPU's own
+    # NUMA node (when this process is allowed to run there): the copies, not the kernels, set that leg's time
+    numa = bind_to_gpu_numa_node(local_rank)
     host = [t.pin_memory() for t in (q, k, v, do)]
     qd, kd, vd, dod = (t.to(dev) for t in host)
     sinks = sinks.to(dev)
@@ -161,23 +208,9 @@ def run_b200(args, rank, world, local_rank):
     S_pad = _cabi.padded_len(S)
 
     # device-resident buffers for the kernel-level timing (direct C-ABI calls, no allocation inside)
-    o = torch.empty(B, S, Hq, d, dtype=torch.bfloat16, device=dev)
-    lse = torch.empty(B, Hq, S_pad, dtype=torch.float32, device=dev)
-    delta = torch.empty((_cabi.DELTA_PLANES,) + tuple(lse.shape), dtype=torch.float32, device=dev)
-    dq, dk, dv = torch.empty_like(qd), torch.empty_like(kd), torch.empty_like(vd)
-    dsinks = torch.empty(Hq, dtype=torch.float32, device=dev)
-    status = torch.zeros(1, dtype=torch.int32, device=dev)
-    p = _cabi.Params()
-    p.B, p.Hq, p.Hkv, p.S, p.d, p.window, p.scale, p.device = B, Hq, Hkv, S, d, case.window, case.scale, local_rank
     stream = torch.cuda.current_stream(dev)
-    sinks_f32 = sinks.float().contiguous()
-    p.stream, p.status, p.sinks = stream.cuda_stream, status.data_ptr(), sinks_f32.data_ptr()
-    p.seqlens = seqlens.data_ptr() if seqlens is not None else None
-    p.q, p.k, p.v = (_cabi.tensor4(t, "bhsd") for t in (qd, kd, vd))
-    p.o, p.d_o, p.lse, p.delta = _cabi.tensor4(o, "bshd"), _cabi.tensor4(dod, "bshd"), lse.data_ptr(), delta.data_ptr()
-    p.dq, p.dk, p.dv = (_cabi.tensor4(t, "bhsd") for t in (dq, dk, dv))
-    part = torch.empty(int(lib.b200attn_dsinks_scratch_floats(ctypes.byref(p))), dtype=torch.float32, device=dev)
-    p.dsinks, p.dsinks_partial = dsinks.data_ptr(), part.data_ptr()
+    p, keep = resident_problem(lib, qd, kd, vd, dod, sinks, seqlens, case.scale, case.window, local_rank, stream)
+    status = keep["status"]
     stages = [("fwd", lib.b200attn_fwd), ("bwd_preprocess", lib.b200attn_bwd_preprocess),
               ("bwd_dkdv", lib.b200attn_bwd_dkdv), ("bwd_dq", lib.b200attn_bwd_dq),
               ("bwd_dsinks", lib.b200attn_bwd_dsinks)]
@@ -299,6 +332,11 @@ def run_b200(args, rank, world, local_rank):
     stage_ms = {n: tm[2 + i].item() for i, (n, _) in enumerate(stages)}
     ms_step = ms_total / args.steps
 
+    strong = None
+    if world > 1 and not args.no_strong:
+        strong = {name: strong_scaling_record(name, lib, rank, world, local_rank, dev, stream, max(5, min(args.steps, 50)))
+                  for name in ("cfg2", "cfg3")}
+
     if rank != 0:
         if world > 1:
             torch.distributed.destroy_process_group()
@@ -326,7 +364,7 @@ def run_b200(args, rank, world, local_rank):
     roof["frac"] = round(roof["achieved"] / roof["peak"], 4)
     roof["kernel"] = top
     roof["peak_source"] = peaks["source"]
-    roof["traffic"] = NCU_TRAFFIC_BYTES.get((args.workload, top))
+    roof["traffic"] = ncu_traffic_bytes(args.workload, top)
     t_min = max(by["total"] / (peaks["hbm_gbs"] * 1e9), fl["total"] / (peaks["bf16_tflops"] * 1e12))
 
     line = {
@@ -347,26 +385,161 @@ def run_b200(args, rank, world, local_rank):
         "gpu_launches": len(stages) * args.steps,
         "roofline": roof,
         "kernels": kernels,
+        "host_numa": numa,
     }
+    if strong is not None:
+        line["strong"] = strong
+    if world == 1 and not args.no_contender:
+        line["triton_reference"] = triton_contender(args, case, (qd, kd, vd, dod, sinks), seqlens, stream)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_sample(args.workload, budget_s=args.cpu_budget)
+        line["cpu_baseline_cfg1"] = cpu_hf_eager_cfg1()
     print(json.dumps(line), flush=True)
     if world > 1:
         torch.distributed.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (workload, kernel) -> bytes; absent = not captured.
-NCU_TRAFFIC_BYTES: dict = {
-    # cfg3 launches = 4x the rows of the captured B=1, S=8192, window-128 case (traffic grows with rows)
-    ("cfg3", "fwd"): 4 * (83_966_464 + 23_717_632),
-    ("cfg3", "bwd_dkdv"): 4 * (167_820_800 + 11_823_872),
-    ("cfg3", "bwd_dq"): 4 * (155_429_120 + 38_473_216),
-    # cfg2 launches = 4x the rows of the captured B=1, S=4096 full-causal case
-    ("cfg2", "fwd"): 4 * (42_022_144 + 2_042_112),
-    ("cfg2", "bwd_dkdv"): 4 * (84_045_568 + 5_633_536),
-    ("cfg2", "bwd_dq"): 4 * (77_636_096 + 10_991_872),
-}
+def ncu_traffic_bytes(workload, kernel):
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch of `kernel` on `workload`, from the ncu
+    captures summarised in profiles/ncu_traffic.json (absent entry = not captured: null)."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "ncu_traffic.json")) as f:
+            entry = json.load(f)["traffic"].get(workload, {}).get(kernel)
+        return None if entry is None else int(entry["dram_read_bytes"]) + int(entry["dram_write_bytes"])
+    except Exception:
+        return None
+
+
+def bind_to_gpu_numa_node(gpu_index: int) -> dict:
+    """Restrict this process to the CPUs of the NUMA node the GPU hangs off, if it may run there.
+
+    Pinned host memory is placed on the node of the thread that first touches it; with several ranks
+    staging gigabytes per step, buffers on the far socket halve the copy bandwidth.  Best effort: any
+    failure (no sysfs entry, node outside the allowed CPU set) leaves the affinity as it was.
+    """
+    info = {"gpu_node": None, "bound": False}
+    try:
+        bus = torch.cuda.get_device_properties(gpu_index).pci_bus_id
+        dom = torch.cuda.get_device_properties(gpu_index).pci_domain_id
+        devn = torch.cuda.get_device_properties(gpu_index).pci_device_id
+        with open(f"/sys/bus/pci/devices/{dom:04x}:{bus:02x}:{devn:02x}.0/numa_node") as f:
+            node = int(f.read().strip())
+        info["gpu_node"] = node
+        if node < 0:
+            return info
+        with open(f"/sys/devices/system/node/node{node}/cpulist") as f:
+            cpus = set()
+            for part in f.read().strip().split(","):
+                lo, _, hi = part.partition("-")
+                cpus.update(range(int(lo), int(hi or lo) + 1))
+        allowed = os.sched_getaffinity(0)
+        target = cpus & allowed
+        info["allowed_cpus"] = len(allowed)
+        if target and target != allowed:
+            os.sched_setaffinity(0, target)
+            info["bound"] = True
+        elif target:
+            info["bound"] = "already local"
+    except Exception as e:
+        info["note"] = f"{type(e).__name__}"
+    return info
+
+
+def time_steps(fn, steps, stream, warm=3):
+    """Average ms per call of fn: warm-up calls first (JIT compilation excluded), CUDA events on `stream`."""
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        fn()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / steps
+
+
+def triton_contender(args, case, tensors, seqlens, stream):
+    """The reference's Triton kernel on this GPU: same device-resident inputs, forward+backward through its own
+    autograd function; this library timed the same way (through `attention()`) right after it."""
+    from baseline import triton_ref
+    from oracle import algorithmic_flops
+    from oregon_gpt_oss_patching_b200.attention_kernel import attention
+    mod, where = triton_ref.load(args.reference_path or None)
+    if mod is None:
+        return {"unavailable": where}
+    q, k, v, do, sinks = tensors
+    sinks_model = sinks.to(torch.bfloat16)     # the attention module holds its sinks in the model dtype
+    steps = max(3, min(args.steps, 20))
+    try:
+        ms_ref = time_steps(lambda: triton_ref.fwd_bwd(mod, q, k, v, do, sinks_model, case.scale, case.window), steps, stream)
+    except Exception as e:
+        return {"unavailable": f"the reference kernel did not run here: {type(e).__name__}: {str(e)[:160]}"}
+
+    def b200_step():
+        qq, kk, vv, ss = (t.detach().requires_grad_(True) for t in (q, k, v, sinks_model))
+        attention(qq, kk, vv, ss, case.scale, case.window, seqlens).backward(do)
+
+    ms_b200 = time_steps(b200_step, steps, stream)
+    fl = algorithmic_flops(case)["total"]
+    return {"ms_per_step": round(ms_ref, 4), "tflops": round(fl / ms_ref / 1e9, 2),
+            "b200_same_protocol_ms": round(ms_b200, 4), "vs_b200": round(ms_ref / ms_b200, 3),
+            "steps": steps, "where": os.path.relpath(where, ROOT) if where.startswith(ROOT) else where,
+            "protocol": "device-resident bf16 inputs, fwd+bwd through each implementation's autograd function, "
+                        "3 warm-up calls (JIT excluded), CUDA events; the reference ignores padding masks"}
+
+
+def strong_scaling_record(name, lib, rank, world, local_rank, dev, stream, steps):
+    """One named configuration sharded by KV-head group over the ranks: total work fixed, no collective.
+
+    Every rank builds the same seeded inputs on its own GPU, takes its groups (all batches), and runs the five
+    kernels on that share; the time is the max over ranks, the throughput the configuration's algorithmic
+    flops over that time.
+    """
+    import ctypes
+    from oracle import CONFIGS, algorithmic_flops
+    from oregon_gpt_oss_patching_b200 import _cabi
+    from oregon_gpt_oss_patching_b200.sharding import shard_by_group
+    import torch.distributed as dist
+    case = CONFIGS[name]
+    if world > case.Hkv or case.Hkv % world:
+        return {"unavailable": f"{world} ranks do not divide {case.Hkv} KV-head groups"}
+    g = torch.Generator(device=dev).manual_seed(case.seed)
+    mk = lambda *shape: (torch.randn(*shape, generator=g, device=dev, dtype=torch.float32) * case.input_scale).to(torch.bfloat16)
+    q, k, v = mk(case.B, case.Hq, case.S, case.d), mk(case.B, case.Hkv, case.S, case.d), mk(case.B, case.Hkv, case.S, case.d)
+    do = mk(case.B, case.S, case.Hq, case.d)
+    sinks = torch.randn(case.Hq, generator=g, device=dev)
+    (qs, ks, vs, dos, ss), (g0, g1) = shard_by_group(q, k, v, do, sinks, rank, world)
+    p, keep = resident_problem(lib, qs, ks, vs, dos, ss, None, case.scale, case.window, local_rank, stream)
+    fns = (lib.b200attn_fwd, lib.b200attn_bwd_preprocess, lib.b200attn_bwd_dkdv, lib.b200attn_bwd_dq, lib.b200attn_bwd_dsinks)
+
+    def step():
+        for fn in fns:
+            rc = fn(ctypes.byref(p))
+            if rc != 0:
+                raise RuntimeError(_cabi.strerror(rc))
+
+    for _ in range(3):
+        step()
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(dev)
+    dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1) / steps], dtype=torch.float64, device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if keep["status"].item() != 0:
+        raise RuntimeError("a kernel abandoned a bounded wait (status word non-zero)")
+    ms = t.item()
+    fl = algorithmic_flops(case)["total"]
+    return {"scaling": "strong", "ms_per_step": round(ms, 5), "value": round(fl / ms / 1e9, 2), "unit": "TFLOP/s",
+            "groups_per_rank": g1 - g0, "steps": steps,
+            "note": "whole configuration split by KV-head group, max over ranks, inputs resident"}
 
 
 # --------------------------------------------------------------------------------------------
@@ -421,6 +594,36 @@ def cpu_sample(workload, budget_s=15.0):
                                       f"fp32 blockwise eager oracle, {dt:.2f} s"}
 
 
+def cpu_hf_eager_cfg1(runs: int = 5) -> dict:
+    """The CPU path the reference project falls back to, unmodified: `transformers`' eager_attention_forward
+    (models/gpt_oss/modeling_gpt_oss.py:245-273) in fp32, forward + autograd backward, on the CPU-runnable
+    configuration exactly (B=1, S=512, 64/8 heads, window 128).  Median of `runs` after one warm-up run."""
+    import types
+    from oracle import CONFIGS, algorithmic_flops, make_inputs, visible_mask
+    try:
+        from transformers.models.gpt_oss.modeling_gpt_oss import eager_attention_forward
+    except Exception as e:
+        return {"unavailable": f"transformers' gpt_oss model cannot be imported: {type(e).__name__}"}
+    case = CONFIGS["cfg1"]
+    threads = use_all_host_threads()
+    q, k, v, do, sinks = make_inputs(case, dtype=torch.float32, device="cpu")
+    vis = visible_mask(case.S, case.window)[None, None]
+    add = torch.zeros(1, 1, case.S, case.S).masked_fill(~vis, torch.finfo(torch.float32).min)
+    times = []
+    for i in range(runs + 1):
+        qq, kk, vv, ss = (t.clone().requires_grad_(True) for t in (q, k, v, sinks))
+        module = types.SimpleNamespace(num_key_value_groups=case.Hq // case.Hkv, sinks=ss, training=False)
+        t0 = time.perf_counter()
+        o, _ = eager_attention_forward(module, qq, kk, vv, add, scaling=case.scale, dropout=0.0)
+        o.backward(do)
+        if i > 0:
+            times.append(time.perf_counter() - t0)
+    med = statistics.median(times)
+    return {"value": round(algorithmic_flops(case)["total"] / med / 1e12, 6), "unit": "TFLOP/s", "ms": round(med * 1e3, 2),
+            "cores": threads, "os_cpu_count": os.cpu_count(), "kind": "reference",
+            "sample": f"cfg1 whole (B=1 S=512 window 128, fp32), transformers eager_attention_forward fwd+bwd, median of {runs}"}
+
+
 def run_reference(args, rank):
     if rank != 0:
         return
@@ -452,6 +655,7 @@ def run_reference(args, rank):
             "cpu_baseline": {"value": round(value, 5), "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                              "kind": "port", "sample": sample},
             "e2e": {"value": round(value, 5), "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "cpu_baseline_cfg1": cpu_hf_eager_cfg1(),
             "gpu_launches": 0}
     print(json.dumps(line), flush=True)
 
@@ -467,6 +671,10 @@ def main():
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--shape", default="", help="B,S,window: run this shape instead of a named workload")
     ap.add_argument("--capture", action="store_true", help="only run warmup+steps passes of the kernels (for ncu)")
+    ap.add_argument("--reference-path", default="", help="directory holding the reference's attention_kernel.py "
+                    "(default: $REFERENCE_PATH, then baseline/_ref)")
+    ap.add_argument("--no-contender", action="store_true", help="skip the reference-Triton-kernel arm")
+    ap.add_argument("--no-strong", action="store_true", help="skip the sharded (strong-scaling) records at N > 1")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

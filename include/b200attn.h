@@ -25,7 +25,9 @@
  *   - Masking: key j is visible to query i of sequence b iff j <= i, j > i - window (when
  *     window > 0) and j < seqlens[b]; rows i >= seqlens[b] are padding (o = 0, no gradient).
  *     The reference ignores padding (attention_kernel.py:348-358); seqlens == NULL gives
- *     exactly its behaviour.
+ *     exactly its behaviour.  Padding rows of q, k, v and dO are still read (they share tiles
+ *     with real rows) and enter the tensor-core products with a zero weight, so they must hold
+ *     FINITE values: anything finite leaves every result bit-identical, Inf/NaN there do not.
  */
 #ifndef B200ATTN_H_
 #define B200ATTN_H_
@@ -53,6 +55,16 @@ enum {
   B200ATTN_ESCRATCH = -8,    /* scratch buffer missing or too small               */
   B200ATTN_ETOOLARGE = -9    /* larger than b200attn_bwd_static_scratch can take  */
 };
+
+/* Bits of the `status` word.  Kernels only ever OR bits in.
+ *   B200ATTN_STATUS_WAIT_TIMEOUT   a bounded device-side wait (on a TMA copy or a tensor-core
+ *                                  completion) ran out; the CTA gave up, freed its tensor memory
+ *                                  and returned, results of that call are undefined.
+ *   B200ATTN_STATUS_NONPREFIX_MASK not set by the library itself: the Python binding ORs it in
+ *                                  when a padding mask is not right-padded (a real token after a
+ *                                  padding token), which `seqlens` cannot express. */
+#define B200ATTN_STATUS_WAIT_TIMEOUT 1
+#define B200ATTN_STATUS_NONPREFIX_MASK 2
 
 /* Largest B * Hq * b200attn_padded_len(S) that b200attn_bwd_static_scratch accepts. */
 #define B200ATTN_STATIC_MAX_ROWS (1 << 18)
@@ -177,6 +189,15 @@ int b200attn_bwd_static_scratch(const b200attn_params* p);
  */
 int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int32_t* status, int device,
                            void* stream);
+
+/*
+ * Self-test of the bounded waits, used by the test-suite.  No counterpart in the reference.
+ * One CTA sets up as the attention kernels do (barriers, tensor memory), then every thread waits
+ * on a barrier nothing arrives at, giving up after `wait_limit_cycles` SM cycles (1 ..
+ * 100 000 000, i.e. at most ~50 ms): the kernel must OR B200ATTN_STATUS_WAIT_TIMEOUT into
+ * *status, release its tensor memory and return normally.  Never leaves anything waiting.
+ */
+int b200attn_wait_selftest(int64_t wait_limit_cycles, int32_t* status, int device, void* stream);
 
 #ifdef __cplusplus
 }

@@ -16,11 +16,12 @@ DELTA_PLANES = 10   # B200ATTN_DELTA_PLANES of include/b200attn.h: fp32-sized va
 EXPORTS = (
     "b200attn_version", "b200attn_sizeof_params", "b200attn_strerror", "b200attn_padded_len", "b200attn_dsinks_scratch_floats",
     "b200attn_fwd", "b200attn_bwd", "b200attn_bwd_preprocess", "b200attn_bwd_dsinks", "b200attn_bwd_dkdv",
-    "b200attn_bwd_dq", "b200attn_bwd_static_scratch", "b200attn_umma_selftest",
+    "b200attn_bwd_dq", "b200attn_bwd_static_scratch", "b200attn_umma_selftest", "b200attn_wait_selftest",
 )
 
 ROW_TILE = 128
-STATUS_WAIT_TIMEOUT = 1
+STATUS_WAIT_TIMEOUT = 1      # B200ATTN_STATUS_WAIT_TIMEOUT
+STATUS_NONPREFIX_MASK = 2    # B200ATTN_STATUS_NONPREFIX_MASK
 
 
 class Tensor4(ctypes.Structure):
@@ -85,6 +86,8 @@ def load() -> ctypes.CDLL:
         lib.b200attn_umma_selftest.restype = ctypes.c_int
         lib.b200attn_umma_selftest.argtypes = [ctypes.c_int, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p,
                                                ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        lib.b200attn_wait_selftest.restype = ctypes.c_int
+        lib.b200attn_wait_selftest.argtypes = [ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         _lib = lib
     return _lib
 

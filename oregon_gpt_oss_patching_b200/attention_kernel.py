@@ -32,7 +32,8 @@ import torch
 
 from . import _cabi
 
-__all__ = ["attention", "b200_flash_attention", "triton_flash_attention", "seqlens_from_mask", "last_status"]
+__all__ = ["attention", "b200_flash_attention", "triton_flash_attention", "seqlens_from_mask", "last_status",
+           "check_status"]
 
 _status_words: dict = {}
 
@@ -48,9 +49,29 @@ def _status_word(device: torch.device) -> torch.Tensor:
 
 
 def last_status(device=None) -> int:
-    """Synchronise and return the device status word (0 = no kernel ever gave up a wait)."""
+    """Synchronise and return the device status word.
+
+    0 = nothing went wrong so far; bit ``_cabi.STATUS_WAIT_TIMEOUT`` = a kernel gave up a bounded
+    wait; bit ``_cabi.STATUS_NONPREFIX_MASK`` = a padding mask that is not right-padded was passed.
+    """
     device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
     return int(_status_word(device).item())
+
+
+def check_status(device=None) -> None:
+    """Synchronise and raise ``RuntimeError`` if the device status word is non-zero (then clear it)."""
+    device = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    code = last_status(device)
+    if code == 0:
+        return
+    _status_word(device).zero_()
+    what = []
+    if code & _cabi.STATUS_WAIT_TIMEOUT:
+        what.append("a kernel abandoned a bounded wait")
+    if code & _cabi.STATUS_NONPREFIX_MASK:
+        what.append("an attention mask was not right-padded (a real token follows a padding token): "
+                    "only prefix masks can be reduced to sequence lengths")
+    raise RuntimeError(f"b200attn status {code}: " + "; ".join(what or ["unknown status bits"]))
 
 
 def _as_view(t: torch.Tensor) -> torch.Tensor:
@@ -66,7 +87,11 @@ def seqlens_from_mask(attention_mask: Optional[torch.Tensor], B: int, S: int) ->
     """Valid length of each right-padded sequence as an int32 device tensor, or None.
 
     Accepts a (B,S) keep-mask (bool or 0/1) or HF's additive (B,1,S,S) mask, where position i
-    is a real token iff it may attend to itself (mask[b,0,i,i] == 0).  No host synchronisation.
+    is a real token iff it may attend to itself (mask[b,0,i,i] == 0).  No host synchronisation:
+    a mask that is NOT right-padded (left padding, packed documents -- a real token after a
+    padding token) cannot be expressed as a length; it is detected on the device and reported
+    through the status word (``_cabi.STATUS_NONPREFIX_MASK``), which ``check_status`` /
+    ``B200ATTN_CHECK_STATUS=1`` turn into an exception.
     """
     if attention_mask is None:
         return None
@@ -80,6 +105,9 @@ def seqlens_from_mask(attention_mask: Optional[torch.Tensor], B: int, S: int) ->
         raise ValueError(f"attention_mask must be 2-D or 4-D, got shape {tuple(m.shape)}")
     if keep.shape[0] != B or keep.shape[-1] != S:
         raise ValueError(f"attention_mask shape {tuple(attention_mask.shape)} does not match B={B}, S={S}")
+    if keep.is_cuda and S > 1:
+        bad = (keep[:, 1:] & ~keep[:, :-1]).any()
+        _status_word(keep.device).bitwise_or_(bad.to(torch.int32) * _cabi.STATUS_NONPREFIX_MASK)
     return keep.sum(dim=-1, dtype=torch.int32).contiguous()
 
 
@@ -169,9 +197,7 @@ class _attention(torch.autograd.Function):
 def _maybe_check_status(device) -> None:
     # Opt-in (it synchronises): turn a device-side give-up into an exception right away.
     if os.environ.get("B200ATTN_CHECK_STATUS") == "1":
-        code = last_status(device)
-        if code != 0:
-            raise RuntimeError(f"b200attn kernel abandoned a bounded wait (status {code})")
+        check_status(device)
 
 
 attention = _attention.apply

@@ -5,6 +5,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "attn_common.cuh"
@@ -141,10 +142,20 @@ KernelArgs make_args(const b200attn_params* p) {
   return a;
 }
 
-template <typename Kernel>
-int set_smem(Kernel kernel, size_t bytes) {
-  return cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) == cudaSuccess
-             ? B200ATTN_OK : B200ATTN_ECUDA;
+// Raises a kernel's dynamic shared-memory limit.  The attribute belongs to the (kernel, device) pair and
+// never changes afterwards, so it is set once per pair instead of on every launch.
+constexpr int kMaxDevices = 64;
+template <auto kKernel>
+int set_smem(size_t bytes) {
+  static std::atomic<bool> done[kMaxDevices];   // one array per kernel; zero-initialised
+  int device = -1;
+  if (cudaGetDevice(&device) != cudaSuccess) return B200ATTN_ECUDA;
+  const bool cacheable = device >= 0 && device < kMaxDevices;
+  if (cacheable && done[device].load(std::memory_order_acquire)) return B200ATTN_OK;
+  if (cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
+    return B200ATTN_ECUDA;
+  if (cacheable) done[device].store(true, std::memory_order_release);
+  return B200ATTN_OK;
 }
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ECUDA; }
@@ -195,7 +206,7 @@ int b200attn_fwd(const b200attn_params* p) {
     // short work items (measured cross-over near 4096 keys): the persistent kernel, one CTA per SM
     // walking the items, hides the per-item set-up and first-load latency that dominate them
     const size_t smem = sizeof(FwdSmem) + 1024;
-    if ((rc = set_smem(attn_fwd_persistent_kernel, smem))) return rc;
+    if ((rc = set_smem<attn_fwd_persistent_kernel>(smem))) return rc;
     int n_sm = 0;
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
     const long long n_items = (long long)(a.S_pad / kTile) * p->B * (p->Hq / heads_per_item);
@@ -204,7 +215,7 @@ int b200attn_fwd(const b200attn_params* p) {
     return launch_status();
   }
   const size_t smem = sizeof(FwdOneSmem) + 1024;
-  if ((rc = set_smem(attn_fwd_kernel, smem))) return rc;
+  if ((rc = set_smem<attn_fwd_kernel>(smem))) return rc;
   dim3 grid(a.S_pad / kTile, p->Hq / heads_per_item, p->B);
   attn_fwd_kernel<<<grid, kFwdThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, a);
   return launch_status();
@@ -246,10 +257,10 @@ int b200attn_bwd_dkdv(const b200attn_params* p) {
   dim3 grid(a.S_pad / kTile, p->Hkv, p->B);
   if (p->window > 0 && p->window <= 2 * kTile) {
     // narrow window: most tiles are partly masked, skipping the chunks nobody sees pays
-    if ((rc = set_smem(attn_bwd_dkdv_kernel<true>, smem))) return rc;
+    if ((rc = set_smem<attn_bwd_dkdv_kernel<true>>(smem))) return rc;
     attn_bwd_dkdv_kernel<true><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
   } else {
-    if ((rc = set_smem(attn_bwd_dkdv_kernel<false>, smem))) return rc;
+    if ((rc = set_smem<attn_bwd_dkdv_kernel<false>>(smem))) return rc;
     attn_bwd_dkdv_kernel<false><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
   }
   return launch_status();
@@ -272,7 +283,7 @@ int b200attn_bwd_dq(const b200attn_params* p) {
     if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
     if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
     const size_t smem = sizeof(DqpSmem) + 1024;
-    if ((rc = set_smem(attn_bwd_dq_persistent_kernel, smem))) return rc;
+    if ((rc = set_smem<attn_bwd_dq_persistent_kernel>(smem))) return rc;
     int n_sm = 0;
     if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
     const long long n_items = (long long)(a.S_pad / kTile) * p->B * p->Hq;
@@ -283,7 +294,7 @@ int b200attn_bwd_dq(const b200attn_params* p) {
   if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
   const size_t smem = sizeof(DqSmem) + 1024;
-  if ((rc = set_smem(attn_bwd_dq_kernel, smem))) return rc;
+  if ((rc = set_smem<attn_bwd_dq_kernel>(smem))) return rc;
   attn_bwd_dq_kernel<<<grid, kDqThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tk, tv, a);
   return launch_status();
 }
@@ -305,7 +316,6 @@ static __device__ __align__(256) float g_static_delta[B200ATTN_DELTA_PLANES * kS
 static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 16];  // 8 partials per 128 rows
 
 namespace {
-constexpr int kMaxDevices = 64;
 std::mutex g_static_mutex;
 float* g_static_delta_ptr[kMaxDevices] = {};
 float* g_static_partial_ptr[kMaxDevices] = {};
@@ -357,9 +367,23 @@ int b200attn_umma_selftest(int mode, const void* a, const void* b, float* d, int
   if ((rc = make_map(&ta, ta_view, 1, 1, 128, kTile))) return rc;
   if ((rc = make_map(&tb, tb_view, 1, 1, 128, kTile))) return rc;
   const size_t smem = sizeof(SelftestSmem) + 1024;
-  if ((rc = set_smem(umma_selftest_kernel, smem))) return rc;
+  if ((rc = set_smem<umma_selftest_kernel>(smem))) return rc;
   umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(ta, tb, mode, static_cast<const __nv_bfloat16*>(a),
-                                                                                       static_cast<const __nv_bfloat16*>(b), d, status);
+                                                                                       static_cast<const __nv_bfloat16*>(b), d, status, 0);
+  return launch_status();
+}
+
+int b200attn_wait_selftest(int64_t wait_limit_cycles, int32_t* status, int device, void* stream) {
+  if (status == nullptr || wait_limit_cycles <= 0 || wait_limit_cycles > 100000000ll) return B200ATTN_EINVAL;
+  int rc = check_device(device);
+  if (rc) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  CUtensorMap unused{};   // the waiting mode touches no tensor map
+  const size_t smem = sizeof(SelftestSmem) + 1024;
+  if ((rc = set_smem<umma_selftest_kernel>(smem))) return rc;
+  umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(unused, unused, 3, nullptr, nullptr, nullptr, status,
+                                                                            (long long)wait_limit_cycles);
   return launch_status();
 }
 

@@ -75,7 +75,8 @@ constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s of SM clock: far b
 // kept off the fast path: the first polls read no clock at all (reading %globaltimer costs
 // on the order of a microsecond, which on a per-tile dependency chain is the whole budget),
 // later ones look at the SM cycle counter and the abort flag once every 256 polls.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                long long limit_cycles) {
 #pragma unroll 1
   for (int it = 0; it < 256; ++it)
     if (mbar_try_wait(bar, parity)) return true;
@@ -85,12 +86,15 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitLimitCycles) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }
     }
   }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return mbar_wait_limit(bar, parity, abort_flag, kWaitLimitCycles);
 }
 
 // Short bounded wait used while abandoning a CTA: lets copies that are still in flight land.

@@ -6,6 +6,11 @@
 //                                                     memory read N-contiguous
 //   mode 2: mode 0 plus one more k-step, A[:, :16] * B[:, :16]^T, from unswizzled (rows x 16)
 //           side operands written by the threads (the form the dK/dV kernel's row constants take)
+//   mode 3: no copy, no MMA: every thread waits, with the short limit `wait_limit_cycles`, on a barrier
+//           that nothing will ever arrive at.  The wait must run out, the first thread to notice raises
+//           the CTA's abort flag, the others leave at their next look at it, the CTA reports
+//           kStatusWaitTimeout, frees its tensor memory and returns normally -- the give-up path every
+//           kernel of the library shares, exercised without leaving anything waiting on the GPU.
 #pragma once
 #include "attn_common.cuh"
 
@@ -24,7 +29,8 @@ struct SelftestSmem {
 
 __global__ void __launch_bounds__(128)
 umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b, int mode,
-                     const __nv_bfloat16* a_global, const __nv_bfloat16* b_global, float* d, int* status) {
+                     const __nv_bfloat16* a_global, const __nv_bfloat16* b_global, float* d, int* status,
+                     long long wait_limit_cycles) {
   extern __shared__ uint8_t smem_raw[];
   SelftestSmem* sm = reinterpret_cast<SelftestSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int tid = threadIdx.x, warp = tid >> 5;
@@ -48,6 +54,18 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
   tc_fence_after_sync();
   const uint32_t tmem = sm->tmem_base;
   const uint32_t lane_addr = uint32_t(warp * 32) << 16;
+
+  if (mode == 3) {
+    const bool done = warp_all(mbar_wait_limit(bar_mma, 0, abort_flag, wait_limit_cycles));
+    if (!done && tid == 0 && status != nullptr) atomicOr(status, kStatusWaitTimeout);
+    tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 0) {
+      __syncwarp();
+      tmem_dealloc(tmem, kCols);
+    }
+    return;
+  }
 
   if (tid == 0) {
     if (mode != 1) {

@@ -11,6 +11,31 @@ from oregon_gpt_oss_patching_b200.attention_kernel import attention, last_status
 TOL_TENSOR = 2e-2   # O, dQ, dK, dV
 TOL_DSINKS = 1e-2   # dSinks
 TOL_LSE = 2e-3      # LSE is fp32 output computed from bf16 inputs
+# The whole-tensor measure is dominated by the largest rows (the first rows of a causal layer, whose
+# outputs are single values, are ~100x larger than late rows that average thousands).  So every
+# tensor is also held to a bound relative to its OWN neighbourhood: per (batch, head, 128 positions)
+# tile, max|a-b| over the tile / max|b| over the tile.  A kernel that got only deep key-tile
+# iterations or late query tiles wrong cannot hide behind the early rows' magnitude.
+TOL_TILE = 3e-2
+
+
+def tile_rel_err(a: torch.Tensor, b: torch.Tensor, pos_dim: int, tile: int = 128) -> float:
+    """max over (batch, head, 128-position) tiles of max|a-b|_tile / max|b|_tile.
+
+    a, b: 4-D with the head_dim last and positions along `pos_dim` (1 for (B,S,H,d), 2 for (B,H,S,d)).
+    Tiles whose reference is (almost) all zero are measured against 1e-3 of the global maximum instead.
+    """
+    a = a.float().movedim(pos_dim, 2)      # (B, H, S, d)
+    b = b.float().movedim(pos_dim, 2)
+    B, H, S, d = b.shape
+    pad = (-S) % tile
+    if pad:
+        a = torch.nn.functional.pad(a, (0, 0, 0, pad))
+        b = torch.nn.functional.pad(b, (0, 0, 0, pad))
+    err = (a - b).abs().reshape(B, H, -1, tile * d).amax(dim=-1)
+    den = b.abs().reshape(B, H, -1, tile * d).amax(dim=-1)
+    floor = 1e-3 * float(b.abs().max())
+    return float((err / den.clamp_min(max(floor, 1e-30))).max())
 
 
 def run_b200(q, k, v, do, sinks, scale, window, seqlens=None):
@@ -37,13 +62,21 @@ def assert_close_valid(res, ref, lens, S, tol=TOL_TENSOR, tol_ds=TOL_DSINKS):
         for b, L in enumerate(lens):
             got = res[key][b, :L] if kind == "bshd" else res[key][b, :, :L]
             want = ref[key][b, :L] if kind == "bshd" else ref[key][b, :, :L]
-            worst = max(worst, (got.float().cpu().double() - want.cpu().double()).abs().max().item() / denom)
+            worst = max(worst, (got.float() - want.to(got.device).float()).abs().max().item() / denom)
             pad = res[key][b, L:] if kind == "bshd" else res[key][b, :, L:]
             assert pad.numel() == 0 or float(pad.float().abs().max()) == 0.0, f"{key}: padding rows not zero"
         errs[key] = worst
     for key in ("o", "dq", "dk", "dv"):
         assert errs[key] < tol, (key, errs)
     assert errs["dsinks"] < tol_ds, errs
+    # the same four tensors tile by tile (padding rows are exactly zero on both sides, so they add nothing)
+    dev = res["o"].device
+    for key, pos_dim in (("o", 1), ("dq", 2), ("dk", 2), ("dv", 2)):
+        want = ref[key].to(dev).clone()
+        for b, L in enumerate(lens):   # the oracle's padding rows are zero as well; make that explicit
+            (want[b, L:] if pos_dim == 1 else want[b, :, L:]).zero_()
+        errs[key + "_tile"] = tile_rel_err(res[key], want, pos_dim)
+        assert errs[key + "_tile"] < TOL_TILE, (key, errs)
     assert not any(torch.isnan(res[k_].float()).any().item() for k_ in res), "NaN in results"
     return errs
 
