@@ -139,7 +139,7 @@ int b200attn_bwd(const b200attn_params* p);
  * (attention_kernel.py:102-120).  Reads o, dO, lse; writes delta. */
 int b200attn_bwd_preprocess(const b200attn_params* p);
 
-/* dsinks[h] = sum of the per-warp partials the dq stage wrote (fixed order, warp-shuffle tree:
+/* dsinks[h] = sum of the partials the dq stage wrote (fixed order, warp-shuffle tree:
  * deterministic, unlike the reference's atomics at attention_kernel.py:176).  Must run after
  * b200attn_bwd_dq.  Reads dsinks_partial; writes dsinks. */
 int b200attn_bwd_dsinks(const b200attn_params* p);
@@ -151,7 +151,8 @@ int b200attn_bwd_dkdv(const b200attn_params* p);
 
 /* dq: one CTA owns a 128-row query tile of one head (attention_kernel.py:214-217).  Also writes
  * the sink-gradient partials -sum_i exp(sink - lse_i) * sum_j P_ij dP_ij of its rows
- * (attention_kernel.py:173-175) to dsinks_partial.  Reads q,k,v,dO,lse,delta,sinks. */
+ * (attention_kernel.py:173-175) to dsinks_partial (a fixed number per head and 128 positions, which depends
+ * on the kernel variant the problem selects; b200attn_dsinks_scratch_floats covers every variant).  Reads q,k,v,dO,lse,delta,sinks. */
 int b200attn_bwd_dq(const b200attn_params* p);
 
 /*

@@ -37,7 +37,8 @@ struct KernelArgs {
   float* lse;                       // (B,Hq,S_pad), natural log
   float* delta;                     // (B,Hq,S_pad)
   float* dsinks;                    // (Hq)
-  float* dsinks_partial;            // (Hq, B * S_pad/128)
+  float* dsinks_partial;            // (Hq, B * S_pad/128 * partials_per_tile)
+  int partials_per_tile;            // sink-gradient partials the dQ kernel in use writes per (head, 128 positions)
   StridedPtr o, d_o, dq, dk, dv;    // tensors touched with plain loads/stores
   StridedPtr q, k, v;
 };

@@ -11,9 +11,11 @@
 #include "attn_common.cuh"
 #include "bwd_dkdv_kernel.cuh"
 #include "bwd_dq_kernel.cuh"
+#include "bwd_dq_packed_kernel.cuh"
 #include "bwd_dq_persistent_kernel.cuh"
 #include "bwd_preprocess_kernel.cuh"
 #include "fwd_kernel.cuh"
+#include "fwd_packed_kernel.cuh"
 #include "umma_selftest.cuh"
 
 namespace {
@@ -71,15 +73,15 @@ int check_tensor(const b200attn_tensor& t, int B, int H, int S) {
   return B200ATTN_OK;
 }
 
-// 4-D bf16 map (d, S, H, B) with a (64 x rows) box and the 128-byte swizzle.
-int make_map(CUtensorMap* map, const b200attn_tensor& t, int B, int H, int S, int box_rows) {
+// 4-D bf16 map (d, S, H, B) with a (64 x rows x heads) box and the 128-byte swizzle.
+int make_map(CUtensorMap* map, const b200attn_tensor& t, int B, int H, int S, int box_rows, int box_heads = 1) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return B200ATTN_ECUDA;
   const int64_t ss = usable_stride(t.stride_s, S, kHeadDim), sh = usable_stride(t.stride_h, H, (int64_t)S * ss),
                 sb = usable_stride(t.stride_b, B, (int64_t)S * ss);
   cuuint64_t dims[4] = {(cuuint64_t)kHeadDim, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
   cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
-  cuuint32_t box[4] = {(cuuint32_t)kHeadDim, (cuuint32_t)box_rows, 1, 1};
+  cuuint32_t box[4] = {(cuuint32_t)kHeadDim, (cuuint32_t)box_rows, (cuuint32_t)box_heads, 1};
   cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -122,6 +124,8 @@ int validate(const b200attn_params* p, int need) {
   return check_device(p->device);
 }
 
+bool packed_window_layer(const b200attn_params* p);
+
 KernelArgs make_args(const b200attn_params* p) {
   KernelArgs a{};
   a.B = p->B; a.Hq = p->Hq; a.Hkv = p->Hkv; a.S = p->S;
@@ -137,6 +141,7 @@ KernelArgs make_args(const b200attn_params* p) {
   a.delta = p->delta;
   a.dsinks = p->dsinks;
   a.dsinks_partial = p->dsinks_partial;
+  a.partials_per_tile = packed_window_layer(p) ? kDqPkPartialsPerTile : 8;
   a.o = strided(p->o); a.d_o = strided(p->d_o); a.dq = strided(p->dq); a.dk = strided(p->dk); a.dv = strided(p->dv);
   a.q = strided(p->q); a.k = strided(p->k); a.v = strided(p->v);
   return a;
@@ -156,6 +161,11 @@ int set_smem(size_t bytes) {
     return B200ATTN_ECUDA;
   if (cacheable) done[device].store(true, std::memory_order_release);
   return B200ATTN_OK;
+}
+
+// Layers the head-packed kernels serve: a causal window of at most 128 keys with 8 query heads per KV head.
+bool packed_window_layer(const b200attn_params* p) {
+  return p->window > 0 && p->window <= kPkMaxWindow && p->Hq / p->Hkv == kPkHeads;
 }
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ECUDA; }
@@ -188,7 +198,7 @@ int64_t b200attn_padded_len(int64_t S) { return (S + B200ATTN_ROW_TILE - 1) / B2
 
 int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p) {
   if (p == nullptr) return 0;
-  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 8;
+  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 16;
 }
 
 int b200attn_fwd(const b200attn_params* p) {
@@ -197,10 +207,26 @@ int b200attn_fwd(const b200attn_params* p) {
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
   CUtensorMap tq, tk, tv;
+  const KernelArgs a = make_args(p);
+  if (packed_window_layer(p)) {
+    // the GPT-OSS sliding-window layer: tiles of 8 heads x 16 positions, one 144-key product per tile
+    if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
+    if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kPkKvRows))) return rc;
+    if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kPkKvRows))) return rc;
+    CUtensorMap to;
+    if ((rc = make_map(&to, p->o, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
+    const size_t smem = sizeof(FwdPkSmem) + 1024;
+    if ((rc = set_smem<attn_fwd_packed_kernel>(smem))) return rc;
+    int n_sm = 0;
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
+    const long long n_items = (long long)(a.S_pad / kPkItemPos) * p->B * p->Hkv;
+    const unsigned grid = (unsigned)(n_items < n_sm ? n_items : n_sm);
+    attn_fwd_packed_kernel<<<grid, kFwdPkThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, to, a);
+    return launch_status();
+  }
   if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kTile))) return rc;
   if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
-  const KernelArgs a = make_args(p);
   const int heads_per_item = (a.group % 2 == 0) ? 2 : 1;  // two heads of a KV group share staged K/V tiles
   if (p->window > 0 && p->window <= 32 * kTile) {
     // short work items (measured cross-over near 4096 keys): the persistent kernel, one CTA per SM
@@ -273,6 +299,23 @@ int b200attn_bwd_dq(const b200attn_params* p) {
   if (!guard.ok) return B200ATTN_ECUDA;
   CUtensorMap tk, tv;
   const KernelArgs a = make_args(p);
+  if (packed_window_layer(p)) {
+    // the GPT-OSS sliding-window layer: tiles of 8 heads x 16 positions, one 144-key product per tile
+    CUtensorMap tq, tdo, tdq;
+    if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
+    if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
+    if ((rc = make_map(&tdq, p->dq, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
+    if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kPkKvRows))) return rc;
+    if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kPkKvRows))) return rc;
+    const size_t smem = sizeof(DqPkSmem) + 1024;
+    if ((rc = set_smem<attn_bwd_dq_packed_kernel>(smem))) return rc;
+    int n_sm = 0;
+    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
+    const long long n_items = (long long)(a.S_pad / kPkItemPos) * p->B * p->Hkv;
+    const unsigned pgrid = (unsigned)(n_items < n_sm ? n_items : n_sm);
+    attn_bwd_dq_packed_kernel<<<pgrid, kDqPkThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tdo, tk, tv, tdq, a);
+    return launch_status();
+  }
   dim3 grid(a.S_pad / kTile, p->Hq, p->B);
   if (p->window > 0 && p->window <= 8 * kTile) {
     // short work items (at most nine key tiles per query tile; measured cross-over between 1024 and 2048
@@ -313,7 +356,7 @@ int b200attn_bwd(const b200attn_params* p) {
 // library holds these ~10.6 MB until the process exits.
 constexpr int64_t kStaticMaxRows = B200ATTN_STATIC_MAX_ROWS;
 static __device__ __align__(256) float g_static_delta[B200ATTN_DELTA_PLANES * kStaticMaxRows];   // delta | -lse*log2(e) | side tiles
-static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 16];  // 8 partials per 128 rows
+static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 8];  // 16 partials per 128 rows
 
 namespace {
 std::mutex g_static_mutex;

@@ -95,7 +95,7 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
 __global__ void __launch_bounds__(256) attn_bwd_dsinks_kernel(const KernelArgs a) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int h = blockIdx.x;
-  const int n = a.B * (a.S_pad / kTile) * 8;  // eight warp partials per query tile
+  const int n = a.B * (a.S_pad / kTile) * a.partials_per_tile;  // the dQ kernel's partials per query tile
   const float* src = a.dsinks_partial + (long long)h * n;
   float s = 0.f;
   for (int idx = tid; idx < n; idx += 256) s += src[idx];

@@ -14,16 +14,19 @@ TOL_LSE = 2e-3      # LSE is fp32 output computed from bf16 inputs
 # The whole-tensor measure is dominated by the largest rows (the first rows of a causal layer, whose
 # outputs are single values, are ~100x larger than late rows that average thousands).  So every
 # tensor is also held to a bound relative to its OWN neighbourhood: per (batch, head, 128 positions)
-# tile, max|a-b| over the tile / max|b| over the tile.  A kernel that got only deep key-tile
-# iterations or late query tiles wrong cannot hide behind the early rows' magnitude.
+# tile (with at least 32 real positions), max|a-b| over the tile / max|b| over the tile.  A kernel that got only
+# deep key-tile iterations or late query tiles wrong cannot hide behind the early rows' magnitude.
 TOL_TILE = 3e-2
 
 
-def tile_rel_err(a: torch.Tensor, b: torch.Tensor, pos_dim: int, tile: int = 128) -> float:
+def tile_rel_err(a: torch.Tensor, b: torch.Tensor, pos_dim: int, lens=None, tile: int = 128, min_rows: int = 32) -> float:
     """max over (batch, head, 128-position) tiles of max|a-b|_tile / max|b|_tile.
 
     a, b: 4-D with the head_dim last and positions along `pos_dim` (1 for (B,S,H,d), 2 for (B,H,S,d)).
-    Tiles whose reference is (almost) all zero are measured against 1e-3 of the global maximum instead.
+    Only tiles holding at least `min_rows` real positions of their sequence count: a tile with one or two
+    rows is measured against those rows alone, and a single row whose gradient is a small difference of large
+    terms (dS = P (dP - delta) with P near 1, delta from the bf16-rounded O) is legitimately off by several
+    per cent of ITSELF in any bf16 implementation while being tiny in absolute terms.
     """
     a = a.float().movedim(pos_dim, 2)      # (B, H, S, d)
     b = b.float().movedim(pos_dim, 2)
@@ -34,8 +37,13 @@ def tile_rel_err(a: torch.Tensor, b: torch.Tensor, pos_dim: int, tile: int = 128
         b = torch.nn.functional.pad(b, (0, 0, 0, pad))
     err = (a - b).abs().reshape(B, H, -1, tile * d).amax(dim=-1)
     den = b.abs().reshape(B, H, -1, tile * d).amax(dim=-1)
-    floor = 1e-3 * float(b.abs().max())
-    return float((err / den.clamp_min(max(floor, 1e-30))).max())
+    n_tiles = err.shape[2]
+    lens = [S] * B if lens is None else lens
+    starts = torch.arange(n_tiles, device=b.device) * tile
+    rows = torch.stack([(int(L) - starts).clamp(0, tile) for L in lens])          # (B, n_tiles) real rows per tile
+    ok = (rows >= min(min_rows, max(int(L) for L in lens)))[:, None, :].expand_as(err)
+    ratio = torch.where(ok & (den > 0), err / den.clamp_min(1e-30), torch.zeros_like(err))
+    return float(ratio.max())
 
 
 def run_b200(q, k, v, do, sinks, scale, window, seqlens=None):
@@ -50,8 +58,11 @@ def run_b200(q, k, v, do, sinks, scale, window, seqlens=None):
     return {"o": o.detach(), "dq": q.grad, "dk": k.grad, "dv": v.grad, "dsinks": s.grad}
 
 
-def assert_close_valid(res, ref, lens, S, tol=TOL_TENSOR, tol_ds=TOL_DSINKS):
-    """Compare on rows inside each sequence (padding rows: o and dq must be exactly zero)."""
+def assert_close_valid(res, ref, lens, S, tol=TOL_TENSOR, tol_ds=TOL_DSINKS, tol_tile=TOL_TILE):
+    """Compare on rows inside each sequence (padding rows: o and dq must be exactly zero).
+
+    tol_tile=None skips the tile-by-tile bound: for inputs scaled until the softmax is one-hot, dS = P (dP - delta)
+    is a difference of nearly equal numbers in every row and no bf16 implementation holds a per-tile bound."""
     errs = {}
     for key in ("dk", "dv"):
         errs[key] = rel_err(res[key].float(), ref[key])
@@ -71,12 +82,12 @@ def assert_close_valid(res, ref, lens, S, tol=TOL_TENSOR, tol_ds=TOL_DSINKS):
     assert errs["dsinks"] < tol_ds, errs
     # the same four tensors tile by tile (padding rows are exactly zero on both sides, so they add nothing)
     dev = res["o"].device
-    for key, pos_dim in (("o", 1), ("dq", 2), ("dk", 2), ("dv", 2)):
+    for key, pos_dim in (("o", 1), ("dq", 2), ("dk", 2), ("dv", 2)) if tol_tile is not None else ():
         want = ref[key].to(dev).clone()
         for b, L in enumerate(lens):   # the oracle's padding rows are zero as well; make that explicit
             (want[b, L:] if pos_dim == 1 else want[b, :, L:]).zero_()
-        errs[key + "_tile"] = tile_rel_err(res[key], want, pos_dim)
-        assert errs[key + "_tile"] < TOL_TILE, (key, errs)
+        errs[key + "_tile"] = tile_rel_err(res[key], want, pos_dim, lens)
+        assert errs[key + "_tile"] < tol_tile, (key, errs)
     assert not any(torch.isnan(res[k_].float()).any().item() for k_ in res), "NaN in results"
     return errs
 

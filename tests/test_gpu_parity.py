@@ -159,7 +159,19 @@ def test_large_sink_and_extreme_logits_stay_finite():
     sinks = torch.tensor([60.0, -60.0, 0.0, 5.0], device=DEV)
     res = run_b200(q, k, v, do, sinks, case.scale, 0)
     ref = oracle_on_gpu(q, k, v, do, sinks, case.scale, 0)
-    assert_close_valid(res, ref, [256], 256)
+    assert_close_valid(res, ref, [256], 256, tol_tile=None)
+
+
+def test_packed_window_layer_with_extreme_sinks_and_logits():
+    """The 8-heads-per-group, window-128 kernels exponentiate against the sink logit and redo rows that would
+    overflow: logits far above and far below the sink, and an early sequence end, must all come out right."""
+    case = AttnCase("t", B=2, S=700, Hq=16, Hkv=2, window=128, seed=31, input_scale=4.0, seqlens=(700, 333))
+    q, k, v, do, _ = make_inputs(case, dtype=torch.bfloat16, device=DEV)
+    sinks = torch.tensor([60.0, -60.0, 0.0, 5.0, -120.0, 120.0, 30.0, -30.0] * 2, device=DEV)
+    res = run_b200(q, k, v, do, sinks, case.scale, 128, case.seqlens)
+    ref = oracle_on_gpu(q, k, v, do, sinks, case.scale, 128, case.seqlens)
+    assert_close_valid(res, ref, case.lengths(), 700, tol_tile=None)
+    assert last_status(DEV) == 0
 
 
 # ---- the benchmark configurations at full size ------------------------------------------------
