@@ -15,25 +15,37 @@
 // at its own 16-row offset (two swizzle atoms, so the UMMA descriptors just start 2 KB later).  Per
 // sub-tile:
 //     S = Q K^T  (M=128, N=144, K=64)   tcgen05.mma, fp32 in tensor memory
-//     P = 2^(S*scale*log2e - m)         one thread per row, all 144 scores in registers; m = the head's sink
-//                                       logit (any m gives the same result as long as nothing overflows; a row
-//                                       whose sum does overflow -- logits ~100 above the sink -- is redone with
-//                                       m = its true maximum), so the common path needs no row-maximum pass
+//     P = 2^(S*scale*log2e - m)         one thread per row; m = the head's sink logit (any m gives the same
+//                                       result as long as nothing overflows; a row whose sum does overflow --
+//                                       logits ~100 above the sink -- is redone with m = its true maximum),
+//                                       so the common path needs no pass for the row maximum
 //     O = P V    (M=128, N=64, K=144)   P as bf16 A operand from tensor memory
 //     O / (sum P + 2^(sink - m)),  LSE = m + log(...)       (attention_kernel.py:53-98 of the reference)
-// The exponentials are the bottleneck of this layer (144 per row against 276 + 441 tensor-pipe cycles per
-// sub-tile), so the two sub-tiles take turns at them: while one runs them the other's MMAs, loads, stores
-// and epilogue proceed.  S of a sub-tile's next item is issued as soon as its S is in registers (S and P have
-// columns of their own); the two sub-tiles share ONE O accumulator, which they use strictly in turn.
-// O rows leave through shared memory and one TMA store per sub-tile, issued by an otherwise idle warp: a
-// thread's row is 128 contiguous bytes 8 KB from its neighbour's, and as plain stores those cost 3000
-// cycles of the load/store unit per item -- more than everything else together.
+//
+// What shapes the code (counters of earlier versions: ~1 of the 2-3 busy warps per scheduler always stalled on
+// "no instruction", the special-function unit 25 % busy, removing the exponentials altogether -4 %):
+//   * Instruction fetch.  A fully unrolled 144-column row is ~25 KB of straight-line code executed once per
+//     item; with two or three such roles per scheduler the instruction cache holds none of it and every phase
+//     runs at a quarter of its issue rate.  So the row is a ROLLED loop over 32-column chunks streamed from
+//     tensor memory (load chunk c+1, exponentials of chunk c, store 16 packed columns of P): a few hundred
+//     instructions that stay hot (16-column chunks pay the pipeline's fill and drain nine times a row and
+//     were half as fast).
+//   * MMA issue.  A separate issuing warp next to busy compute warps gets few issue slots, and every
+//     hand-over costs a barrier round trip (~400 cycles from "P written" to "P V issued" + ~800 to issue).
+//     Here thread 0 of each softmax warpgroup issues its sub-tile's MMAs itself, right after the warpgroup's
+//     P is complete: P V of this item, then S of the next item behind it (the pipe runs them in order).
+//   * Output.  A thread's O row is 128 contiguous bytes 8 KB from its neighbour's; as plain stores that costs
+//     3000 cycles of the load/store unit per item.  Rows go to shared memory and leave with one TMA store per
+//     sub-tile, issued by an otherwise idle warp.
+// The two sub-tiles run freely side by side (two warps per scheduler in their exponentials together get 13 %
+// more out of the special-function unit than one after the other: 2700 against 2 x 1530 cycles for a pair of
+// rows in isolation, so turn-taking costs more than it saves here) and share ONE O accumulator, which they
+// use strictly in turn.
 //
 // Persistent: one CTA per SM walks the items (consecutive CTAs take consecutive position blocks of the same
 // (batch, group), so neighbouring K/V windows meet in L2); Q is double-buffered and K/V go through a 3-stage
-// TMA ring that runs ahead across items.  Warp roles: warps 0-3 / 4-7 softmax of sub-tile A / B, warp 8 / 10
-// lane 0 issue A's / B's MMAs, warp 9 lane 0 every TMA load, warp 11 lane 0 every TMA store.  Every wait is
-// bounded.
+// TMA ring that runs ahead across items.  384 threads: warps 0-3 / 4-7 softmax + MMA issue + epilogue of
+// sub-tile A / B, warp 9 lane 0 every TMA load, warp 11 lane 0 every TMA store.  Every wait is bounded.
 #pragma once
 #include "attn_common.cuh"
 #include "fwd_kernel.cuh"   // exponential helpers, setmaxnreg helpers
@@ -45,6 +57,7 @@ constexpr int kPkHeads = 8;                      // query heads per sub-tile = t
 constexpr int kPkItemPos = 2 * kPkPos;           // positions per work item (two sub-tiles)
 constexpr int kPkMaxWindow = 128;
 constexpr int kPkKeys = kPkMaxWindow + kPkPos;   // 144 key columns per sub-tile
+constexpr int kPkChunks = kPkKeys / 16;          // 9 chunks of 16 columns
 constexpr int kPkKvRows = kPkMaxWindow + kPkItemPos;   // 160 staged K (and V) rows per item
 constexpr int kPkKvBytes = kPkKvRows * kHeadDim * 2;   // 20 KB
 constexpr int kPkSubOffsetBytes = kPkPos * kHeadDim * 2;   // sub-tile B's keys start 16 rows = 2 KB into the block
@@ -64,13 +77,11 @@ struct FwdPkSmem {
   uint64_t bar_kv_full[kPkStages];
   uint64_t bar_kv_empty[kPkStages];       // both sub-tiles' MMAs on a stage retired              (2 x tcgen05.commit)
   uint64_t bar_s_full[2];                 // S of sub-tile X ready                                (tcgen05.commit)
-  uint64_t bar_s_empty[2];                // S of sub-tile X copied into registers                (128 arrivals)
   uint64_t bar_p_full[2];                 // P of sub-tile X written                              (128 arrivals)
   uint64_t bar_pv_done[2];                // P V of sub-tile X retired: O current, P free         (tcgen05.commit)
   uint64_t bar_o_free;                    // O read by an epilogue; phase u = 2 * item + sub-tile (128 arrivals)
   uint64_t bar_ost_full[2];               // O rows of sub-tile X are in shared memory            (128 arrivals)
   uint64_t bar_ost_free[2];               // the TMA store has read them                          (1 arrival)
-  uint64_t bar_exp[2];                    // sub-tile X may run its exponentials                  (128 arrivals of the other)
   uint32_t tmem_base;
   int abort_flag;
   int loads_issued;                       // items whose loads the loader has issued (for the abort drain)
@@ -157,6 +168,48 @@ __device__ __forceinline__ void pk_exp16(const uint32_t (&sc)[16], float2 scale2
   }
 }
 
+// One 16-column chunk of a row: P = 2^(S*scale*log2e - m) for the columns whose bit is set, 0 for the others,
+// packed to bf16 and stored to 8 tensor-memory columns; the row sum grows by the chunk's.  The mask work is
+// skipped when the whole warp sees all 16 columns, the exponentials when it sees none.
+__device__ __forceinline__ void pk_softmax_chunk16(uint32_t (&sc)[16], uint32_t bits, float2 scale2, float2 neg_m2,
+                                                   float2 (&sum)[4], uint32_t tmem_p) {
+  uint32_t pk[8];
+  if (__all_sync(0xffffffffu, bits == 0u)) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e) pk[e] = 0u;
+  } else {
+    if (!__all_sync(0xffffffffu, bits == 0xffffu)) {
+#pragma unroll
+      for (int e = 0; e < 16; ++e) sc[e] = (bits >> e) & 1u ? sc[e] : 0xff800000u;   // -inf
+    }
+    pk_exp16(sc, scale2, neg_m2, pk, sum);
+  }
+  tmem_st8(tmem_p, pk);
+}
+// The same for a 32-column chunk (16 packed columns of P).
+__device__ __forceinline__ void pk_softmax_chunk32(uint32_t (&sc)[32], uint32_t bits, float2 scale2, float2 neg_m2,
+                                                   float2 (&sum)[4], uint32_t tmem_p) {
+  uint32_t pk[16];
+  const int kind = fwd_chunk_kind(bits);
+  if (kind == kChunkNone) {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) pk[e] = 0u;
+  } else {
+    if (kind == kChunkSome) fwd_mask_bits(sc, bits);
+    float unused_mx[4];
+    fwd_exp_chunk<false>(sc, scale2, neg_m2, pk, sum, unused_mx);
+  }
+  tmem_st16(tmem_p, pk);
+}
+// Maximum of the visible columns of a 16-column chunk.
+__device__ __forceinline__ float pk_masked_max16(const uint32_t (&sc)[16], uint32_t bits) {
+  float mx = -INFINITY;
+#pragma unroll
+  for (int e = 0; e < 16; e += 2)
+    mx = fmax3(mx, (bits >> e) & 1u ? __uint_as_float(sc[e]) : -INFINITY, (bits >> (e + 1)) & 1u ? __uint_as_float(sc[e + 1]) : -INFINITY);
+  return mx;
+}
+
 __global__ void __launch_bounds__(kFwdPkThreads, 1)
 attn_fwd_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                        const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
@@ -182,12 +235,10 @@ attn_fwd_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     }
     for (int x = 0; x < 2; ++x) {
       mbar_init(smem_u32(&sm->bar_s_full[x]), 1);
-      mbar_init(smem_u32(&sm->bar_s_empty[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_p_full[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_pv_done[x]), 1);
       mbar_init(smem_u32(&sm->bar_ost_full[x]), kComputeThreads);
       mbar_init(smem_u32(&sm->bar_ost_free[x]), 1);
-      mbar_init(smem_u32(&sm->bar_exp[x]), kComputeThreads);
     }
     mbar_init(smem_u32(&sm->bar_o_free), kComputeThreads);
     sm->abort_flag = 0;
@@ -253,76 +304,22 @@ attn_fwd_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       if (!ok) report_abort(a);
     }
     __syncwarp();
-  } else if (warp == 8 || warp == 10) {
-    // -------------------- MMA issuer of sub-tile A (warp 8) / sub-tile B (warp 10) --------------------
-    const int x = (warp - 8) >> 1;
-    if (lane == 0) {
-      const uint32_t idesc_qk = make_idesc_bf16(kTile, kPkKeys, 0, 0);
-      const uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, 0, 1);
-      const uint32_t tmem_s = tmem + x * kFwdPkColS, tmem_p = tmem + kFwdPkColP + x * kFwdPkColPStride, tmem_o = tmem + kFwdPkColO;
-      const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
-                     bar_p = smem_u32(&sm->bar_p_full[x]), bar_pv = smem_u32(&sm->bar_pv_done[x]),
-                     bar_of = smem_u32(&sm->bar_o_free);
-      bool ok = true;
-      PkItem it;
-      int k = 0;
-      bool have = pk_next_item(a, k, n_items, dv, it);
-      // S of item n: Q and K landed, and the softmax threads hold S of item n-1 in registers
-      auto issue_s = [&](int n) -> bool {
-        const int qb = n & 1, s = n % kPkStages;
-        if (n >= 1 && !mbar_wait(bar_se, (n - 1) & 1, abort_flag)) return false;
-        if (!mbar_wait(smem_u32(&sm->bar_q_full[qb]), (n >> 1) & 1, abort_flag)) return false;
-        if (!mbar_wait(smem_u32(&sm->bar_kv_full[s]), (n / kPkStages) & 1, abort_flag)) return false;
-        tc_fence_after_sync();
-        const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[qb][x]));
-        const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]) + x * kPkSubOffsetBytes);
-#pragma unroll
-        for (int kk = 0; kk < kHeadDim / 16; ++kk)
-          umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
-        umma_commit(bar_s);
-        umma_commit(smem_u32(&sm->bar_q_empty[qb]));   // Q is free once both sub-tiles' S MMAs retire
-        return true;
-      };
-      if (have) ok = issue_s(0);
-      for (int n = 0; ok && have; ++n) {
-        ++k;
-        have = pk_next_item(a, k, n_items, dv, it);
-        // S of the next item first: it only waits for this item's S to be in registers, so it is computed
-        // underneath this item's exponentials
-        if (have && !(ok = issue_s(n + 1))) break;
-        // O = P V of item n: P written, and O's previous contents (the other sub-tile's, use u-1) read
-        if (!(ok = mbar_wait(bar_p, n & 1, abort_flag))) break;
-        const int u = 2 * n + x;
-        if (u >= 1 && !(ok = mbar_wait(bar_of, (u - 1) & 1, abort_flag))) break;
-        tc_fence_after_sync();
-        const int s = n % kPkStages;
-        const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s]) + x * kPkSubOffsetBytes);
-#pragma unroll
-        for (int kk = 0; kk < kPkKeys / 16; ++kk)
-          umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, kk > 0);
-        umma_commit(bar_pv);
-        umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // K[s], V[s] are free once both sub-tiles' MMAs on them retire
-      }
-      if (!ok) report_abort(a);
-    }
-    __syncwarp();
   }
   } else {
   setmaxnreg_inc_216_fwd();
   {
-    // -------------------------------------- softmax --------------------------------------
+    // ------------------------- softmax, MMA issue and epilogue of one sub-tile -------------------------
     const int x = warp >> 2;                                      // sub-tile A or B
     const int r = tid & 127;
     const int hl = r >> 4, sp = r & 15;                           // head within the group, position within the sub-tile
     const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;   // this warp's TMEM lane quarter
-    const uint32_t tmem_s_row = tmem + x * kFwdPkColS + lane_addr;
-    const uint32_t tmem_p_row = tmem + kFwdPkColP + x * kFwdPkColPStride + lane_addr;
-    const uint32_t tmem_o_row = tmem + kFwdPkColO + lane_addr;
-    const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_se = smem_u32(&sm->bar_s_empty[x]),
-                   bar_p = smem_u32(&sm->bar_p_full[x]), bar_pv = smem_u32(&sm->bar_pv_done[x]),
-                   bar_of = smem_u32(&sm->bar_o_free), bar_ostf = smem_u32(&sm->bar_ost_full[x]),
-                   bar_oste = smem_u32(&sm->bar_ost_free[x]);
-    const uint32_t bar_exp_mine = smem_u32(&sm->bar_exp[x]), bar_exp_other = smem_u32(&sm->bar_exp[x ^ 1]);
+    const uint32_t tmem_s = tmem + x * kFwdPkColS, tmem_p = tmem + kFwdPkColP + x * kFwdPkColPStride, tmem_o = tmem + kFwdPkColO;
+    const uint32_t tmem_s_row = tmem_s + lane_addr, tmem_p_row = tmem_p + lane_addr, tmem_o_row = tmem_o + lane_addr;
+    const uint32_t bar_s = smem_u32(&sm->bar_s_full[x]), bar_p = smem_u32(&sm->bar_p_full[x]),
+                   bar_pv = smem_u32(&sm->bar_pv_done[x]), bar_of = smem_u32(&sm->bar_o_free),
+                   bar_ostf = smem_u32(&sm->bar_ost_full[x]), bar_oste = smem_u32(&sm->bar_ost_free[x]);
+    const uint32_t idesc_qk = make_idesc_bf16(kTile, kPkKeys, 0, 0);
+    const uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, 0, 1);
     const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
     uint8_t* const o_row_smem = sm->o[x] + r * 128;               // this thread's row of the outgoing O tile
     int n = 0;   // active items so far
@@ -330,151 +327,150 @@ attn_fwd_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     float sink2 = 0.f;
     bool ok = true;
 
-    for (int k = 0;; ++k) {
-      const int id = k * (int)gridDim.x + (int)blockIdx.x;
-      if (id >= n_items) break;
-      const PkItem it = pk_item(a, id, dv);
+    // S of item n of this sub-tile (issued by thread 0 of the warpgroup): Q and K landed.  S of item n-1 has been
+    // read by every thread of the warpgroup (they had written P of item n-1 before this is called).
+    auto issue_s = [&](int n_) -> bool {
+      const int qb = n_ & 1, s = n_ % kPkStages;
+      if (!mbar_wait(smem_u32(&sm->bar_q_full[qb]), (n_ >> 1) & 1, abort_flag)) return false;
+      if (!mbar_wait(smem_u32(&sm->bar_kv_full[s]), (n_ / kPkStages) & 1, abort_flag)) return false;
+      tc_fence_after_sync();
+      const uint64_t q_desc = desc_kmajor(smem_u32(sm->q[qb][x]));
+      const uint64_t k_desc = desc_kmajor(smem_u32(sm->k[s]) + x * kPkSubOffsetBytes);
+#pragma unroll
+      for (int kk = 0; kk < kHeadDim / 16; ++kk)
+        umma_ss(tmem_s, q_desc + kk * kDescKStepKMajor, k_desc + kk * kDescKStepKMajor, idesc_qk, kk > 0);
+      umma_commit(bar_s);
+      umma_commit(smem_u32(&sm->bar_q_empty[qb]));   // Q is free once both sub-tiles' S MMAs retire
+      return true;
+    };
+
+    int k = 0;
+    PkItem it;
+    // padding-only items met on the way get their outputs defined here (no tensor work)
+    auto scan = [&](int& k_, PkItem& it_) -> bool {
+      for (;; ++k_) {
+        const int id = k_ * (int)gridDim.x + (int)blockIdx.x;
+        if (id >= n_items) return false;
+        it_ = pk_item(a, id, dv);
+        if (it_.q0 < it_.len) return true;
+        const int h = it_.g * kPkHeads + hl, i = it_.q0 + x * kPkPos + sp;
+        if (i < a.S) zero_row(a.o.row(it_.b, h, i));
+        a.lse[((long long)(it_.b * a.Hq + h)) * a.S_pad + i] = 0.f;
+      }
+    };
+    bool have = scan(k, it);
+    if (have && r == 0) {
+      if (!issue_s(0)) *abort_flag = 1;
+    }
+    __syncwarp();
+
+#pragma unroll 1
+    while (have) {
       const int h = it.g * kPkHeads + hl;
       const int i = it.q0 + x * kPkPos + sp;                      // this thread's query position
       float* lse_out = a.lse + ((long long)(it.b * a.Hq + h)) * a.S_pad + i;
-      if (it.q0 >= it.len) {  // the item is padding only: define its output, no tensor work
-        if (i < a.S) zero_row(a.o.row(it.b, h, i));
-        *lse_out = 0.f;
-        continue;
-      }
+      const int len = it.len, s_stage = n % kPkStages;
       if (it.g != g_cur) {   // (consecutive items nearly always belong to the same group)
         g_cur = it.g;
         sink2 = a.sinks[h] * kLog2e;
       }
       const int kb = it.q0 + x * kPkPos - kPkMaxWindow;           // key of column 0
-      const PkRowMask rm = pk_row_mask(sp, kb, a.window, it.len);
+      const PkRowMask rm = pk_row_mask(sp, kb, a.window, len);
+      // the next item (its first use is thread 0's S issue, but every thread walks the same sequence)
+      ++k;
+      have = scan(k, it);
 
       if (!(ok = warp_all(mbar_wait(bar_s, n & 1, abort_flag)))) break;
       tc_fence_after_sync();
-      uint32_t s[4][32], s4[16];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) tmem_ld32(tmem_s_row + c * 32, s[c]);
-      tmem_ld16(tmem_s_row + 128, s4);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(bar_se);   // the tensor core may overwrite S with the next item's scores
-      // masks: a chunk all 32 rows of the warp see needs no work, one nobody sees no exponentials
-      int kind[5];
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const uint32_t bits = range_bits(rm.lo - c * 32, rm.hi - c * 32);
-        kind[c] = fwd_chunk_kind(bits);
-        if (kind[c] == kChunkSome) fwd_mask_bits(s[c], bits);
-      }
-      {
-        const uint32_t bits = range_bits(rm.lo - 128, rm.hi - 128) & 0xffffu;   // 16 columns
-        kind[4] = __all_sync(0xffffffffu, bits == 0u) ? kChunkNone : (__all_sync(0xffffffffu, bits == 0xffffu) ? kChunkAll : kChunkSome);
-        if (kind[4] == kChunkSome) {
-#pragma unroll
-          for (int e = 0; e < 16; ++e) s4[e] = (bits >> e) & 1u ? s4[e] : 0xff800000u;
-        }
-      }
-      // the two sub-tiles take turns at the exponentials; sub-tile A goes first (its first wait, parity 1 of a
-      // fresh barrier, passes at once)
-      const uint32_t exp_parity = (x == 0) ? ((n & 1) ^ 1) : (n & 1);
-      if (!(ok = warp_all(mbar_wait(bar_exp_mine, exp_parity, abort_flag)))) break;
-      // P V of this sub-tile's previous item retired before its epilogue ran: the P columns are free
+      // (P V of this sub-tile's previous item retired before its epilogue ran: the P columns are free)
       float m = sink2;
       float l;
-      {
+#pragma unroll 1
+      for (int pass = 0;; ++pass) {
         const float2 neg_m2 = make_float2(-m, -m);
         float2 sum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-        float unused_mx[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-          if (c == 3) mbar_arrive(bar_exp_other);   // hand over early: covers the other side's wake-up latency
-          if (kind[c] == kChunkNone) {
-#pragma unroll
-            for (int e = 0; e < 16; ++e) pk[e] = 0u;
-          } else {
-            fwd_exp_chunk<false>(s[c], scale2, neg_m2, pk, sum, unused_mx);
-          }
-          tmem_st16(tmem_p_row + c * 16, pk);
+        // 32 columns per step (two steps per trip round the loop, the next step's scores in flight under this
+        // step's exponentials), the last 16 columns after the loop
+        uint32_t sa[32], sb[32], st[16];
+        tmem_ld32(tmem_s_row, sa);
+#pragma unroll 1
+        for (int c = 0; c < 4; c += 2) {
+          tmem_wait_ld();
+          tmem_ld32(tmem_s_row + (c + 1) * 32, sb);
+          pk_softmax_chunk32(sa, range_bits(rm.lo - c * 32, rm.hi - c * 32), scale2, neg_m2, sum, tmem_p_row + c * 16);
+          tmem_wait_ld();
+          if (c == 0) tmem_ld32(tmem_s_row + 64, sa); else tmem_ld16(tmem_s_row + 128, st);
+          pk_softmax_chunk32(sb, range_bits(rm.lo - (c + 1) * 32, rm.hi - (c + 1) * 32), scale2, neg_m2, sum, tmem_p_row + (c + 1) * 16);
         }
-        uint32_t pk[8];
-        if (kind[4] == kChunkNone) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) pk[e] = 0u;
-        } else {
-          pk_exp16(s4, scale2, neg_m2, pk, sum);
-        }
-        tmem_st8(tmem_p_row + 64, pk);
+        tmem_wait_ld();
+        pk_softmax_chunk16(st, range_bits(rm.lo - 128, rm.hi - 128) & 0xffffu, scale2, neg_m2, sum, tmem_p_row + 64);
         l = fwd_sum4(sum);
-      }
-      // Scores far above the sink logit (about 100 in the log2 domain) overflow against m = sink: redo such rows
-      // with their true maximum.  A warp-wide decision, taken by next to no warp on real data.
-      if (__any_sync(0xffffffffu, !(l < 1.0e30f))) {
-        float mx = -INFINITY;   // over the chunks somebody sees; masked scores in them are -inf already
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          if (kind[c] != kChunkNone) mx = fmaxf(mx, pk_max32(s[c]));
-        if (kind[4] != kChunkNone) mx = fmaxf(mx, pk_max16(s4));
+        // Scores ~100 (log2 domain) above the sink logit overflow against m = sink: such rows (next to none on
+        // real data; a warp-wide decision) are redone with their true maximum.  S is still in tensor memory.
+        if (pass == 1 || !__any_sync(0xffffffffu, !(l < 1.0e30f))) break;
+        float mx = -INFINITY;
+#pragma unroll 1
+        for (int c = 0; c < kPkChunks; ++c) {
+          tmem_ld16(tmem_s_row + c * 16, st);
+          tmem_wait_ld();
+          mx = fmaxf(mx, pk_masked_max16(st, range_bits(rm.lo - c * 16, rm.hi - c * 16) & 0xffffu));
+        }
         m = fmaxf(sink2, mx * a.scale_log2);   // (a padding row sees nothing: mx = -inf, m = the sink)
-        const float2 neg_m2 = make_float2(-m, -m);
-        float2 sum[4] = {{0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}, {0.f, 0.f}};
-        float unused_mx[4];
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint32_t pk[16];
-          if (kind[c] == kChunkNone) {
-#pragma unroll
-            for (int e = 0; e < 16; ++e) pk[e] = 0u;
-          } else {
-            fwd_exp_chunk<false>(s[c], scale2, neg_m2, pk, sum, unused_mx);
-          }
-          tmem_st16(tmem_p_row + c * 16, pk);
-        }
-        uint32_t pk[8];
-        if (kind[4] == kChunkNone) {
-#pragma unroll
-          for (int e = 0; e < 8; ++e) pk[e] = 0u;
-        } else {
-          pk_exp16(s4, scale2, neg_m2, pk, sum);
-        }
-        tmem_st8(tmem_p_row + 64, pk);
-        l = fwd_sum4(sum);
       }
       tmem_wait_st();
       tc_fence_before_sync();
       mbar_arrive(bar_p);
+
+      if (r == 0) {
+        // ---- thread 0: O = P V of this item, then S of the next item behind it ----
+        bool go = mbar_wait(bar_p, n & 1, abort_flag);                  // the whole warpgroup's P is written
+        const int u = 2 * n + x;
+        if (go && u >= 1) go = mbar_wait(bar_of, (u - 1) & 1, abort_flag);   // O's previous contents (the other sub-tile's) read
+        if (go) {
+          tc_fence_after_sync();
+          const uint64_t v_desc = desc_mnmajor(smem_u32(sm->v[s_stage]) + x * kPkSubOffsetBytes);
+#pragma unroll
+          for (int kk = 0; kk < kPkKeys / 16; ++kk)
+            umma_ts(tmem_o, tmem_p + kk * 8, v_desc + kk * kDescKStepMNMajor, idesc_pv, kk > 0);
+          umma_commit(bar_pv);
+          umma_commit(smem_u32(&sm->bar_kv_empty[s_stage]));   // K[s], V[s] are free once both sub-tiles' MMAs on them retire
+          if (have) go = issue_s(n + 1);
+        }
+        if (!go) *abort_flag = 1;
+      }
+      __syncwarp();
       const float z = l + fast_exp2(sink2 - m);   // the sink joins the denominator only
       const float inv = 1.f / z;
 
+      // ---- epilogue: O rows to shared memory in the layout the TMA store expects (16-byte chunk c of row r at
+      // chunk position c ^ (r % 8)); the store of this sub-tile's previous item must have read the buffer ----
+      const bool st_free = n == 0 || mbar_test_wait(bar_oste, (n - 1) & 1);   // asked early, answered under the wait below
       if (!(ok = warp_all(mbar_wait(bar_pv, n & 1, abort_flag)))) break;
       tc_fence_after_sync();
-      uint32_t o0[32], o1[32];
-      tmem_ld32(tmem_o_row, o0);
-      tmem_ld32(tmem_o_row + 32, o1);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(bar_of);   // the other sub-tile's P V may overwrite O
-      // the row goes to shared memory in the layout the TMA store expects (16-byte chunk c of row r at chunk
-      // position c ^ (r % 8)); the store of this sub-tile's previous item must have read the buffer
-      if (n >= 1 && !(ok = warp_all(mbar_wait(bar_oste, (n - 1) & 1, abort_flag)))) break;
+      if (!warp_all(st_free) && !(ok = warp_all(mbar_wait(bar_oste, (n - 1) & 1, abort_flag)))) break;
+#pragma unroll 1
+      for (int half = 0; half < 2; ++half) {
+        uint32_t o0[32];
+        tmem_ld32(tmem_o_row + half * 32, o0);
+        tmem_wait_ld();
+        if (half == 1) {
+          tc_fence_before_sync();
+          mbar_arrive(bar_of);   // all of O is in registers or shared memory: the other sub-tile's P V may overwrite it
+        }
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        *reinterpret_cast<uint4*>(o_row_smem + ((c ^ (r & 7)) << 4)) =
-            make_uint4(pack_bf16(__uint_as_float(o0[c * 8]) * inv, __uint_as_float(o0[c * 8 + 1]) * inv),
-                       pack_bf16(__uint_as_float(o0[c * 8 + 2]) * inv, __uint_as_float(o0[c * 8 + 3]) * inv),
-                       pack_bf16(__uint_as_float(o0[c * 8 + 4]) * inv, __uint_as_float(o0[c * 8 + 5]) * inv),
-                       pack_bf16(__uint_as_float(o0[c * 8 + 6]) * inv, __uint_as_float(o0[c * 8 + 7]) * inv));
-        *reinterpret_cast<uint4*>(o_row_smem + (((c + 4) ^ (r & 7)) << 4)) =
-            make_uint4(pack_bf16(__uint_as_float(o1[c * 8]) * inv, __uint_as_float(o1[c * 8 + 1]) * inv),
-                       pack_bf16(__uint_as_float(o1[c * 8 + 2]) * inv, __uint_as_float(o1[c * 8 + 3]) * inv),
-                       pack_bf16(__uint_as_float(o1[c * 8 + 4]) * inv, __uint_as_float(o1[c * 8 + 5]) * inv),
-                       pack_bf16(__uint_as_float(o1[c * 8 + 6]) * inv, __uint_as_float(o1[c * 8 + 7]) * inv));
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<uint4*>(o_row_smem + (((half * 4 + c) ^ (r & 7)) << 4)) =
+              make_uint4(pack_bf16(__uint_as_float(o0[c * 8]) * inv, __uint_as_float(o0[c * 8 + 1]) * inv),
+                         pack_bf16(__uint_as_float(o0[c * 8 + 2]) * inv, __uint_as_float(o0[c * 8 + 3]) * inv),
+                         pack_bf16(__uint_as_float(o0[c * 8 + 4]) * inv, __uint_as_float(o0[c * 8 + 5]) * inv),
+                         pack_bf16(__uint_as_float(o0[c * 8 + 6]) * inv, __uint_as_float(o0[c * 8 + 7]) * inv));
       }
       fence_proxy_async_smem();   // written with ordinary stores, read by the TMA engine
       mbar_arrive(bar_ostf);
-      *lse_out = (i < it.len) ? (m + log2f(z)) * kLn2 : 0.f;
+      *lse_out = (i < len) ? (m + log2f(z)) * kLn2 : 0.f;
       ++n;
     }
+    if (!ok && r == 0) report_abort(a);
   }
   }
 
@@ -486,6 +482,7 @@ attn_fwd_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   }
   if (sm->abort_flag && tid == 9 * 32) {
     // abandoned: give copies still in flight a bounded chance to land before shared memory goes away
+    report_abort(a);
     const int issued = sm->loads_issued;
     for (int n = max(0, issued - 2); n < issued; ++n) mbar_wait_drain(smem_u32(&sm->bar_q_full[n & 1]), (n >> 1) & 1);
     for (int n = max(0, issued - kPkStages); n < issued; ++n)

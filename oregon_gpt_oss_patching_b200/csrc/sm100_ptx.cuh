@@ -77,16 +77,17 @@ constexpr long long kWaitLimitCycles = 4000000000ll;  // ~2 s of SM clock: far b
 // later ones look at the SM cycle counter and the abort flag once every 256 polls.
 __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                                 long long limit_cycles) {
-#pragma unroll 1
-  for (int it = 0; it < 256; ++it)
-    if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
+  // one compact loop (this is inlined at every wait of every role; code size is instruction-fetch time)
+  long long t0 = 0;
 #pragma unroll 1
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 255u) == 0u) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > limit_cycles) {
+      const long long t = clock64();
+      if (t0 == 0) {
+        t0 = t;
+      } else if (t - t0 > limit_cycles) {
         *abort_flag = 1;
         return false;
       }
@@ -95,6 +96,41 @@ __device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, v
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
   return mbar_wait_limit(bar, parity, abort_flag, kWaitLimitCycles);
+}
+
+// try_wait with a suspend-time hint: the hardware may keep the thread suspended for up to `hint_ns` before it
+// reports "not yet", so a role that waits for a long time (an epilogue, a loader) does not spin through the
+// issue slots and the shared-memory pipe the working warps need.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t done;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(done)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return done != 0;
+}
+// Bounded wait like mbar_wait, polling through mbar_try_wait_hint.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  long long t0 = 0;
+#pragma unroll 1
+  for (uint32_t it = 1;; ++it) {
+    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
+    if ((it & 15u) == 0u) {
+      if (*abort_flag) return false;
+      const long long t = clock64();
+      if (t0 == 0) {
+        t0 = t;
+      } else if (t - t0 > kWaitLimitCycles) {
+        *abort_flag = 1;
+        return false;
+      }
+    }
+  }
 }
 
 // Short bounded wait used while abandoning a CTA: lets copies that are still in flight land.
