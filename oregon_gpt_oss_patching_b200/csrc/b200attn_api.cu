@@ -198,7 +198,7 @@ int64_t b200attn_padded_len(int64_t S) { return (S + B200ATTN_ROW_TILE - 1) / B2
 
 int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p) {
   if (p == nullptr) return 0;
-  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 16;
+  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 8;
 }
 
 int b200attn_fwd(const b200attn_params* p) {
@@ -356,7 +356,7 @@ int b200attn_bwd(const b200attn_params* p) {
 // library holds these ~10.6 MB until the process exits.
 constexpr int64_t kStaticMaxRows = B200ATTN_STATIC_MAX_ROWS;
 static __device__ __align__(256) float g_static_delta[B200ATTN_DELTA_PLANES * kStaticMaxRows];   // delta | -lse*log2(e) | side tiles
-static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 8];  // 16 partials per 128 rows
+static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 16];  // 8 partials per 128 rows
 
 namespace {
 std::mutex g_static_mutex;

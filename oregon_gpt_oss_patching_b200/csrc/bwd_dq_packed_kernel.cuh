@@ -10,17 +10,26 @@
 //
 // A work item is 32 consecutive positions of one (batch, KV group) = two tiles ("units") that share one
 // staged block of K and V rows [q0-128, q0+32).  Persistent, one CTA per SM; consecutive CTAs take
-// consecutive position blocks, so neighbouring K/V windows meet in L2.  Pipeline over units:
-//   * warp 9 streams Q/dO tiles (double-buffered, one 4-D TMA box {d 64, positions 16, heads 8} each) and
+// consecutive position blocks, so neighbouring K/V windows meet in L2.
+//
+// What shapes the pipeline: with the arithmetic and the MMAs knocked out the first version still took 2800
+// cycles per unit -- the compute warps' own chain of barrier waits, tensor-memory loads and stores, epilogue
+// and bookkeeping, each step a 50-300 cycle latency that nothing hides (the two compute warpgroups work on the
+// same unit in lockstep) -- against 1600 for the arithmetic itself.  So the compute warps do nothing but
+//   load S/dP (72 columns each) -> exponentials and dS -> store dS,
+// and everything else runs beside them:
+//   * warp 13 streams Q/dO tiles (double-buffered, one 4-D TMA box {d 64, positions 16, heads 8} each) and
 //     K/V blocks (3-stage ring) and runs ahead;
-//   * warp 8 issues the S/dP MMAs of unit u+1 as soon as the compute threads hold S/dP of unit u in registers;
-//   * the two compute warpgroups split the 144 key columns (72 each), write dS (bf16) to tensor memory;
-//   * warp 10 issues the dQ MMAs into one of two dQ accumulators, so they never wait for an epilogue;
-//   * the epilogue of unit u (read dQ, scale, sink-gradient partial) runs after the compute of unit u+1, when
-//     its MMAs have long retired; dQ rows leave through shared memory and one TMA store (warp 11), because a
-//     thread's row is 128 contiguous bytes far from its neighbour's and plain stores of that shape keep the
-//     load/store unit busy longer than the arithmetic takes.
-// Every wait is bounded.
+//   * warp 12 issues the S/dP MMAs of unit u+1 as soon as the compute threads hold S/dP of unit u in registers;
+//   * dS is double-buffered in tensor memory and stored chunk by chunk as it is computed, so the compute
+//     threads never wait for the dQ MMAs of the unit before; warp 14 issues those MMAs;
+//   * a third warpgroup (warps 8-11) runs every epilogue: reads dQ, scales, stages the rows in shared memory
+//     for one TMA store (warp 15) -- a thread's row is 128 contiguous bytes far from its neighbour's and plain
+//     stores of that shape keep the load/store unit busy longer than the arithmetic takes -- and reduces the
+//     sink-gradient partial from the per-row sums the compute threads hand over through shared memory.
+// 512 threads; registers after setmaxnreg: compute 2 x 128 x 200, epilogue 128 x 56, the rest 128 x 56
+// (= 512 x 128, the pool the CTA is launched with).  Barrier phases that are certainly complete are asked about
+// early (a test costs 100-300 cycles of latency even then) and only waited for if not.  Every wait is bounded.
 #pragma once
 #include "attn_common.cuh"
 #include "bwd_dq_kernel.cuh"        // dq_compute_chunk
@@ -28,12 +37,12 @@
 
 namespace b200attn {
 
-constexpr int kDqPkThreads = 384;
+constexpr int kDqPkThreads = 512;
 constexpr int kDqPkTmemCols = 512;
 constexpr int kDqPkHalf = kPkKeys / 2;   // 72 key columns per compute warpgroup
-// tensor-memory columns: S [0,144)  dP [144,288)  dS bf16 [288,360)  dQ, two buffers [384,448) [448,512)
-constexpr uint32_t kDqPkColDp = 144, kDqPkColDs = 288, kDqPkColDq = 384;
-constexpr int kDqPkPartialsPerTile = 16;   // sink-gradient partials per (head, 128 positions): 8 units x 2 warpgroups
+// tensor-memory columns: S [0,144)  dP [144,288)  dS bf16, two buffers [288,360) [368,440)  dQ [448,512)
+constexpr uint32_t kDqPkColDp = 144, kDqPkColDs = 288, kDqPkColDsStride = 80, kDqPkColDq = 448;
+constexpr int kDqPkPartialsPerTile = 8;   // sink-gradient partials per (head, 128 positions): one per unit
 
 struct DqPkSmem {
   alignas(1024) uint8_t q[2][kTileBytes];          // [buffer]: the next unit's Q and dO land while this one runs
@@ -47,12 +56,15 @@ struct DqPkSmem {
   uint64_t bar_kv_empty[kPkStages];        // every MMA on a stage retired                     (tcgen05.commit)
   uint64_t bar_s_full;                     // S and dP ready                                   (tcgen05.commit)
   uint64_t bar_s_free;                     // S and dP are in registers                        (256 arrivals)
-  uint64_t bar_p_full;                     // dS written                                       (256 arrivals)
-  uint64_t bar_p_free;                     // the dQ MMAs have read dS                         (tcgen05.commit)
-  uint64_t bar_dq_full[2];                 // the dQ MMAs into a buffer retired                (tcgen05.commit)
-  uint64_t bar_dq_free[2];                 // a dQ buffer read by the epilogue                 (256 arrivals)
-  uint64_t bar_out_full;                   // dQ rows are in shared memory                     (256 arrivals)
+  uint64_t bar_p_full[2];                  // a dS buffer written                              (256 arrivals); one barrier per buffer,
+                                           // so that the writers can never complete two phases unobserved
+  uint64_t bar_p_free[2];                  // the dQ MMAs have read a dS buffer                (tcgen05.commit)
+  uint64_t bar_dq_full;                    // the dQ MMAs of a unit retired                    (tcgen05.commit)
+  uint64_t bar_dq_free;                    // dQ read by the epilogue                          (128 arrivals)
+  uint64_t bar_acc_full;                   // the rows' sink-gradient terms are in shared memory (256 arrivals)
+  uint64_t bar_out_full;                   // dQ rows are in shared memory (and the sink terms read) (128 arrivals)
   uint64_t bar_out_free;                   // the TMA store has read them                      (1 arrival)
+  float acc[2][kTile];                     // [compute warpgroup][row]: -exp(sink - LSE) * sum_j P dP over its columns
   uint32_t tmem_base;
   int abort_flag;
   int loads_issued;                        // items whose K/V loads have been issued (for the abort drain)
@@ -70,20 +82,35 @@ __device__ __forceinline__ void tmem_st4(uint32_t taddr, const uint32_t (&r)[4])
                : "memory");
 }
 
-// dS of 8 key columns (the tail of a warpgroup's 72) for one query row; adds P*dP to acc.  Always with selects.
-__device__ __forceinline__ void dq_compute_chunk8(const uint32_t (&rs)[8], const uint32_t (&rp)[8], float2 scale2, float2 nl22,
-                                                  float2 neg_delta2, uint32_t bits, uint32_t (&pk)[4], float2& acc) {
+// dS (bf16 pairs) of N key columns for one query row from S/dP in registers, stored to N/2 tensor-memory
+// columns at `tmem_ds`; adds sum P*dP to acc.  Masked columns get S = -inf first (P = 0, dS = 0; dP is finite),
+// which is skipped when the whole warp sees all N columns; nothing at all is computed when it sees none.
+template <int N>
+__device__ __forceinline__ void dqpk_chunk(uint32_t (&rs)[N], const uint32_t (&rp)[N], uint32_t bits, float2 scale2, float2 nl22,
+                                           float2 neg_delta2, float2& acc, uint32_t tmem_ds) {
+  constexpr uint32_t kAll = N == 32 ? 0xffffffffu : ((1u << N) - 1u);
+  bits &= kAll;
+  uint32_t pk[N / 2];
+  if (__all_sync(0xffffffffu, bits == 0u)) {
 #pragma unroll
-  for (int e = 0; e < 8; e += 2) {
-    const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2, nl22);
-    float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
-    p.x = (bits >> e) & 1u ? p.x : 0.f;
-    p.y = (bits >> (e + 1)) & 1u ? p.y : 0.f;
-    const float2 dp = make_float2(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1]));
-    acc = __ffma2_rn(p, dp, acc);
-    const float2 ds = __fmul2_rn(p, __fadd2_rn(dp, neg_delta2));
-    pk[e >> 1] = pack_bf16(ds.x, ds.y);
+    for (int e = 0; e < N / 2; ++e) pk[e] = 0u;
+  } else {
+    if (!__all_sync(0xffffffffu, bits == kAll)) {
+#pragma unroll
+      for (int e = 0; e < N; ++e) rs[e] = (bits >> e) & 1u ? rs[e] : 0xff800000u;   // -inf
+    }
+#pragma unroll
+    for (int e = 0; e < N; e += 2) {
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2, nl22);
+      const float2 p = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+      const float2 dp = make_float2(__uint_as_float(rp[e]), __uint_as_float(rp[e + 1]));
+      acc = __ffma2_rn(p, dp, acc);
+      const float2 ds = __fmul2_rn(p, __fadd2_rn(dp, neg_delta2));
+      pk[e >> 1] = pack_bf16(ds.x, ds.y);
+    }
   }
+  if constexpr (N == 16) tmem_st8(tmem_ds, pk);
+  else tmem_st4(tmem_ds, pk);
 }
 
 __global__ void __launch_bounds__(kDqPkThreads, 1)
@@ -99,19 +126,20 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
   const PkDivs dv = pk_divs(a);
   const int n_items = dv.n_chunks * a.B * a.Hkv;
   const float* nlse_base = a.delta + (long long)a.B * a.Hq * a.S_pad;  // plane 1 of the delta scratch
-  const int units_per_head = a.B * (a.S_pad / kPkPos);                  // sink-gradient partial slots: [head][batch][unit][warpgroup]
+  const int units_per_head = a.B * (a.S_pad / kPkPos);                  // sink-gradient partial slots: [head][batch][unit]
 
   const uint32_t bar_s_full = smem_u32(&sm->bar_s_full), bar_s_free = smem_u32(&sm->bar_s_free),
-                 bar_p_full = smem_u32(&sm->bar_p_full), bar_p_free = smem_u32(&sm->bar_p_free),
-                 bar_out_full = smem_u32(&sm->bar_out_full), bar_out_free = smem_u32(&sm->bar_out_free);
+                 bar_dq_full = smem_u32(&sm->bar_dq_full), bar_dq_free = smem_u32(&sm->bar_dq_free),
+                 bar_acc_full = smem_u32(&sm->bar_acc_full), bar_out_full = smem_u32(&sm->bar_out_full),
+                 bar_out_free = smem_u32(&sm->bar_out_free);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
     for (int q = 0; q < 2; ++q) {
       mbar_init(smem_u32(&sm->bar_q_full[q]), 1);
       mbar_init(smem_u32(&sm->bar_q_empty[q]), 1);
-      mbar_init(smem_u32(&sm->bar_dq_full[q]), 1);
-      mbar_init(smem_u32(&sm->bar_dq_free[q]), 2 * kComputeThreads);
+      mbar_init(smem_u32(&sm->bar_p_full[q]), 2 * kComputeThreads);
+      mbar_init(smem_u32(&sm->bar_p_free[q]), 1);
     }
     for (int s = 0; s < kPkStages; ++s) {
       mbar_init(smem_u32(&sm->bar_kv_full[s]), 1);
@@ -119,16 +147,17 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     }
     mbar_init(bar_s_full, 1);
     mbar_init(bar_s_free, 2 * kComputeThreads);
-    mbar_init(bar_p_full, 2 * kComputeThreads);
-    mbar_init(bar_p_free, 1);
-    mbar_init(bar_out_full, 2 * kComputeThreads);
+    mbar_init(bar_dq_full, 1);
+    mbar_init(bar_dq_free, kComputeThreads);
+    mbar_init(bar_acc_full, 2 * kComputeThreads);
+    mbar_init(bar_out_full, kComputeThreads);
     mbar_init(bar_out_free, 1);
     sm->abort_flag = 0;
     sm->loads_issued = 0;
     sm->q_loads_issued = 0;
     fence_mbar_init();
   }
-  if (warp == 8) {
+  if (warp == 12) {
     __syncwarp();
     tmem_alloc(smem_u32(&sm->tmem_base), kDqPkTmemCols);
     tmem_relinquish();
@@ -139,9 +168,9 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
   const uint32_t tmem = sm->tmem_base;
   const uint32_t tmem_s = tmem, tmem_dp = tmem + kDqPkColDp, tmem_ds = tmem + kDqPkColDs, tmem_dq = tmem + kDqPkColDq;
 
-  if (warp >= 8) {
-  setmaxnreg_dec_72();
-  if (warp == 9) {
+  if (warp >= 12) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  if (warp == 13) {
     // ------------------------------------ TMA loader ------------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_q);
@@ -153,6 +182,7 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       int n = 0;   // active items so far (K/V stage = n % kPkStages; units 2n, 2n+1; Q/dO buffer = unit & 1)
       for (int k = 0; ok && pk_next_item(a, k, n_items, dv, it); ++k, ++n) {
         const int s = n % kPkStages;
+#pragma unroll 1
         for (int x = 0; x < 2 && ok; ++x) {
           const int u = 2 * n + x, qb = x;
           if (u >= 2 && !(ok = mbar_wait(smem_u32(&sm->bar_q_empty[qb]), ((u >> 1) - 1) & 1, abort_flag))) break;
@@ -174,7 +204,7 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       if (!ok) report_abort(a);
     }
     __syncwarp();
-  } else if (warp == 11) {
+  } else if (warp == 15) {
     // ------------------------------------ TMA stores of dQ ------------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_dq);
@@ -182,6 +212,7 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       PkItem it;
       int n = 0;
       for (int k = 0; ok && pk_next_item(a, k, n_items, dv, it); ++k, ++n) {
+#pragma unroll 1
         for (int x = 0; x < 2; ++x) {
           const int u = 2 * n + x;
           if (!(ok = mbar_wait(bar_out_full, u & 1, abort_flag))) break;
@@ -195,7 +226,7 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       if (!ok) report_abort(a);
     }
     __syncwarp();
-  } else if (warp == 8) {
+  } else if (warp == 12) {
     // ------------------------- MMA issuer, S and dP (front) -------------------------
     if (lane == 0) {
       const uint32_t idesc_front = make_idesc_bf16(kTile, kPkKeys, 0, 0);    // A, B both K-contiguous, N = 144
@@ -205,6 +236,7 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       for (int k = 0; ok && pk_next_item(a, k, n_items, dv, it); ++k, ++n) {
         const int s = n % kPkStages;
         if (!(ok = mbar_wait(smem_u32(&sm->bar_kv_full[s]), (n / kPkStages) & 1, abort_flag))) break;
+#pragma unroll 1
         for (int x = 0; x < 2; ++x) {
           const int u = 2 * n + x, qb = x;
           if (!(ok = mbar_wait(smem_u32(&sm->bar_q_full[qb]), (u >> 1) & 1, abort_flag))) break;
@@ -227,7 +259,7 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       if (!ok) report_abort(a);
     }
     __syncwarp();
-  } else if (warp == 10) {
+  } else {
     // ------------------------------ MMA issuer, dQ (back) ------------------------------
     if (lane == 0) {
       const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
@@ -236,19 +268,19 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
       int n = 0;
       for (int k = 0; ok && pk_next_item(a, k, n_items, dv, it); ++k, ++n) {
         const int s = n % kPkStages;
+#pragma unroll 1
         for (int x = 0; x < 2; ++x) {
           const int u = 2 * n + x;
-          if (!(ok = mbar_wait(bar_p_full, u & 1, abort_flag))) break;   // dS of the unit written
-          // the dQ buffer is overwritten: the epilogue of the unit before the previous one must have read it
-          if (u >= 2 && !(ok = mbar_wait(smem_u32(&sm->bar_dq_free[u & 1]), ((u >> 1) - 1) & 1, abort_flag))) break;
+          if (!(ok = mbar_wait(smem_u32(&sm->bar_p_full[u & 1]), (u >> 1) & 1, abort_flag))) break;   // dS of the unit written
+          if (u >= 1 && !(ok = mbar_wait(bar_dq_free, (u - 1) & 1, abort_flag))) break;               // dQ of the unit before read
           tc_fence_after_sync();
           const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k[s]) + x * kPkSubOffsetBytes);
-          const uint32_t dq = tmem_dq + (u & 1) * 64;
+          const uint32_t ds = tmem_ds + (u & 1) * kDqPkColDsStride;
 #pragma unroll
           for (int kk = 0; kk < kPkKeys / 16; ++kk)
-            umma_ts(dq, tmem_ds + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, kk > 0 ? 1u : 0u);
-          umma_commit(bar_p_free);                          // dS is reusable once these retire
-          umma_commit(smem_u32(&sm->bar_dq_full[u & 1]));
+            umma_ts(tmem_dq, ds + kk * 8, kt_desc + kk * kDescKStepMNMajor, idesc_back, kk > 0 ? 1u : 0u);
+          umma_commit(smem_u32(&sm->bar_p_free[u & 1]));    // the dS buffer is reusable once these retire
+          umma_commit(bar_dq_full);
           if (x == 1) umma_commit(smem_u32(&sm->bar_kv_empty[s]));   // and so is the K/V stage (its S/dP MMAs retired before dS was written)
         }
         if (!ok) break;
@@ -257,8 +289,61 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     }
     __syncwarp();
   }
+  } else if (warp >= 8) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+  {
+    // ------------------------------------- epilogues --------------------------------------
+    const int r = tid & 127;
+    const int hl = r >> 4, sp = r & 15;   // head within the group, position within the unit
+    const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
+    uint8_t* const out_row = sm->out + r * 128;
+    bool ok = true;
+    PkItem it;
+    int n = 0;
+    for (int k = 0; ok && pk_next_item(a, k, n_items, dv, it); ++k, ++n) {
+#pragma unroll 1
+      for (int x = 0; x < 2; ++x) {
+        const int u = 2 * n + x;
+        const int i = it.q0 + x * kPkPos + sp;
+        const int h = it.g * kPkHeads + hl;
+        // sink gradient of this warp's two heads (16 rows each): the two compute warpgroups' terms, fixed-order tree
+        if (!(ok = warp_all(mbar_wait(bar_acc_full, u & 1, abort_flag)))) break;
+        float dsk = sm->acc[0][r] + sm->acc[1][r];
+#pragma unroll
+        for (int off = 8; off > 0; off >>= 1) dsk += __shfl_xor_sync(0xffffffffu, dsk, off);
+        if (sp == 0) a.dsinks_partial[(long long)h * units_per_head + (long long)it.b * (a.S_pad / kPkPos) + (i >> 4)] = dsk;
+        if (!(ok = warp_all(mbar_wait(bar_dq_full, u & 1, abort_flag)))) break;
+        tc_fence_after_sync();
+        // the store of the previous unit must have read the staging buffer
+        if (u >= 1 && !(ok = warp_all(mbar_wait(bar_out_free, (u - 1) & 1, abort_flag)))) break;
+        const float sc = (i < it.len) ? a.scale : 0.f;
+        // the row goes to shared memory in the layout the TMA store expects: 16-byte chunk c of row r at chunk
+        // position c ^ (r % 8); 32 columns at a time (this warpgroup lives on few registers)
+#pragma unroll 1
+        for (int half = 0; half < 2; ++half) {
+          uint32_t r0[32];
+          tmem_ld32(tmem_dq + lane_addr + half * 32, r0);
+          tmem_wait_ld();
+          if (half == 1) {
+            tc_fence_before_sync();
+            mbar_arrive(bar_dq_free);   // the next unit's dQ MMAs may overwrite dQ
+          }
+#pragma unroll
+          for (int c = 0; c < 4; ++c)
+            *reinterpret_cast<uint4*>(out_row + (((half * 4 + c) ^ (r & 7)) << 4)) =
+                make_uint4(pack_bf16(__uint_as_float(r0[c * 8]) * sc, __uint_as_float(r0[c * 8 + 1]) * sc),
+                           pack_bf16(__uint_as_float(r0[c * 8 + 2]) * sc, __uint_as_float(r0[c * 8 + 3]) * sc),
+                           pack_bf16(__uint_as_float(r0[c * 8 + 4]) * sc, __uint_as_float(r0[c * 8 + 5]) * sc),
+                           pack_bf16(__uint_as_float(r0[c * 8 + 6]) * sc, __uint_as_float(r0[c * 8 + 7]) * sc));
+        }
+        fence_proxy_async_smem();   // written with ordinary stores, read by the TMA engine
+        mbar_arrive(bar_out_full);
+      }
+    }
+    if (!ok && r == 0) report_abort(a);
+  }
   } else {
-  setmaxnreg_inc_216();
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 200;");
   {
     // ------------------------------------- compute --------------------------------------
     const int wg = warp >> 2;             // which 72 key columns of every unit
@@ -267,50 +352,16 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
     const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
     const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
     const int c0 = wg * kDqPkHalf;        // first key column of this thread
-    uint8_t* const out_row = sm->out + r * 128;
     int u = 0;                            // units so far
+    int g_cur = -1;
+    float sink2 = 0.f;                    // this thread's head's sink logit * log2(e), for the group at hand
+    bool s_ready = false;
     bool ok = true;
 
     // row constants of a unit: -LSE * log2(e) and delta of this thread's row
     auto row_off_of = [&](const PkItem& it, int x) -> long long {
       return ((long long)(it.b * a.Hq + it.g * kPkHeads + hl)) * a.S_pad + it.q0 + x * kPkPos + sp;
     };
-
-    // The epilogue of a unit runs after the compute of the next one (see the file comment).
-    bool pending = false;
-    int p_b = 0, p_h = 0, p_i = 0, p_len = 0, p_u = 0;
-    float p_nl2 = 0.f, p_pdp = 0.f;
-    auto epilogue = [&]() -> bool {
-      if (!warp_all(mbar_wait(smem_u32(&sm->bar_dq_full[p_u & 1]), (p_u >> 1) & 1, abort_flag))) return false;
-      // warpgroup 0 takes dQ columns 0-31, warpgroup 1 columns 32-63
-      tc_fence_after_sync();
-      uint32_t r0[32];
-      tmem_ld32(tmem_dq + (p_u & 1) * 64 + lane_addr + wg * 32, r0);
-      tmem_wait_ld();
-      tc_fence_before_sync();
-      mbar_arrive(smem_u32(&sm->bar_dq_free[p_u & 1]));   // the unit after the next may overwrite this dQ buffer
-      // sink gradient of this warp's two heads (16 rows each) for this warpgroup's key columns: fixed-order tree
-      float dsk = (p_i < p_len) ? -fast_exp2(fmaf(a.sinks[p_h], kLog2e, p_nl2)) * p_pdp : 0.f;
-#pragma unroll
-      for (int off = 8; off > 0; off >>= 1) dsk += __shfl_xor_sync(0xffffffffu, dsk, off);
-      if (sp == 0)
-        a.dsinks_partial[((long long)p_h * units_per_head + (long long)p_b * (a.S_pad / kPkPos) + (p_i >> 4)) * 2 + wg] = dsk;
-      // the row goes to shared memory in the layout the TMA store expects (16-byte chunk c of row r at chunk
-      // position c ^ (r % 8)); the store of the previous unit must have read the buffer
-      if (p_u >= 1 && !warp_all(mbar_wait(bar_out_free, (p_u - 1) & 1, abort_flag))) return false;
-      const float sc = (p_i < p_len) ? a.scale : 0.f;
-#pragma unroll
-      for (int c = 0; c < 4; ++c)
-        *reinterpret_cast<uint4*>(out_row + (((wg * 4 + c) ^ (r & 7)) << 4)) =
-            make_uint4(pack_bf16(__uint_as_float(r0[c * 8]) * sc, __uint_as_float(r0[c * 8 + 1]) * sc),
-                       pack_bf16(__uint_as_float(r0[c * 8 + 2]) * sc, __uint_as_float(r0[c * 8 + 3]) * sc),
-                       pack_bf16(__uint_as_float(r0[c * 8 + 4]) * sc, __uint_as_float(r0[c * 8 + 5]) * sc),
-                       pack_bf16(__uint_as_float(r0[c * 8 + 6]) * sc, __uint_as_float(r0[c * 8 + 7]) * sc));
-      fence_proxy_async_smem();   // written with ordinary stores, read by the TMA engine
-      mbar_arrive(bar_out_full);
-      return true;
-    };
-
     // next item at or after round k with real rows; padding-only items met on the way get their outputs here
     auto scan = [&](int& k, PkItem& it) -> bool {
       for (;; ++k) {
@@ -322,110 +373,118 @@ attn_bwd_dq_packed_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid
         for (int x = 0; x < 2; ++x) {
           const int i = it.q0 + x * kPkPos + sp;
           if (wg == 0 && i < a.S) zero_row(a.dq.row(it.b, h, i));   // dQ rows are zero,
-          if (sp == 0) a.dsinks_partial[((long long)h * units_per_head + (long long)it.b * (a.S_pad / kPkPos) + (i >> 4)) * 2 + wg] = 0.f;  // no sink gradient
+          if (wg == 0 && sp == 0) a.dsinks_partial[(long long)h * units_per_head + (long long)it.b * (a.S_pad / kPkPos) + (i >> 4)] = 0.f;  // no sink gradient
         }
       }
     };
 
-    PkItem cur, nxt;
+    // one flat loop over units (unit u = item u/2, half u%2), not unrolled: see the note at the chunk loop
+    PkItem cur;
     int k = 0;
     bool have = scan(k, cur);
-    float nl2[2] = {0.f, 0.f}, delta[2] = {0.f, 0.f};   // per unit of the current item
+    int x = 0;                            // which half of the current item
+    float nl2 = 0.f, delta = 0.f;         // -LSE * log2(e) and delta of this thread's row of the current unit
     if (have) {
-#pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        const long long ro = row_off_of(cur, x);
-        nl2[x] = nlse_base[ro];
-        delta[x] = a.delta[ro];
-      }
+      const long long ro = row_off_of(cur, 0);
+      nl2 = nlse_base[ro];
+      delta = a.delta[ro];
     }
-    while (ok && have) {
-      int k_n = k + 1;
-      const bool have_n = scan(k_n, nxt);
-      float nl2_n[2] = {0.f, 0.f}, delta_n[2] = {0.f, 0.f};   // the next item's row constants: in flight under this item's work
-      if (have_n) {
-#pragma unroll
-        for (int x = 0; x < 2; ++x) {
-          const long long ro = row_off_of(nxt, x);
-          nl2_n[x] = nlse_base[ro];
-          delta_n[x] = a.delta[ro];
-        }
+#pragma unroll 1
+    for (; have; ++u) {
+      if (cur.g != g_cur) {   // (consecutive items nearly always belong to the same group)
+        g_cur = cur.g;
+        sink2 = a.sinks[cur.g * kPkHeads + hl] * kLog2e;
       }
-#pragma unroll
-      for (int x = 0; x < 2; ++x, ++u) {
-        const int i = cur.q0 + x * kPkPos + sp;           // this thread's query position
-        const int kb = cur.q0 + x * kPkPos - kPkMaxWindow;   // key of column 0
-        const PkRowMask rm = pk_row_mask(sp, kb, a.window, cur.len);
-        const float2 nl22 = make_float2(nl2[x], nl2[x]), neg_delta2 = make_float2(-delta[x], -delta[x]);
-        float2 acc = make_float2(0.f, 0.f);   // this warpgroup's share of sum_j P_ij dP_ij, two lanes
+      const int i = cur.q0 + x * kPkPos + sp;              // this thread's query position
+      const int kb = cur.q0 + x * kPkPos - kPkMaxWindow;   // key of column 0
+      const int len = cur.len;
+      const PkRowMask rm = pk_row_mask(sp, kb, a.window, len);
+      const float2 nl22 = make_float2(nl2, nl2), neg_delta2 = make_float2(-delta, -delta);
+      float2 acc = make_float2(0.f, 0.f);   // this warpgroup's share of sum_j P_ij dP_ij, two lanes
+      // the unit after this one: the item's other half, or the first half of the next item with real rows
+      PkItem nxt = cur;
+      bool have_n = true;
+      if (x == 1) {
+        ++k;
+        have_n = scan(k, nxt);
+      }
+      const int x_n = x ^ 1;
 
-        if (!(ok = warp_all(mbar_wait(bar_s_full, u & 1, abort_flag)))) break;
-        tc_fence_after_sync();
-        uint32_t rs[2][32], rp[2][32], rs8[8], rp8[8];
-        tmem_ld32(tmem_s + lane_addr + c0, rs[0]);
-        tmem_ld32(tmem_dp + lane_addr + c0, rp[0]);
-        tmem_ld32(tmem_s + lane_addr + c0 + 32, rs[1]);
-        tmem_ld32(tmem_dp + lane_addr + c0 + 32, rp[1]);
-        tmem_ld8(tmem_s + lane_addr + c0 + 64, rs8);
-        tmem_ld8(tmem_dp + lane_addr + c0 + 64, rp8);
+      // barrier phases needed further down and certainly complete by then: ask now, the answers arrive under
+      // the loads.  The dS buffer was read by the dQ MMAs of the unit before the previous one; the epilogue of
+      // the previous unit has read the sink terms (one slot: the producer may not get two phases ahead).
+      const uint32_t bar_pf = smem_u32(&sm->bar_p_free[u & 1]);
+      const bool p_free = u < 2 || mbar_test_wait(bar_pf, ((u >> 1) - 1) & 1);
+      const bool acc_free = u == 0 || mbar_test_wait(bar_out_full, (u - 1) & 1);
+      if (!warp_all(s_ready) && !(ok = warp_all(mbar_wait(bar_s_full, u & 1, abort_flag)))) break;
+      tc_fence_after_sync();
+      if (!warp_all(p_free) && !(ok = warp_all(mbar_wait(bar_pf, ((u >> 1) - 1) & 1, abort_flag)))) break;
+      tc_fence_after_sync();
+      // the next unit's row constants: a whole unit of arithmetic before their first use
+      float nl2_n = 0.f, delta_n = 0.f;
+      if (have_n) {
+        const long long ro = row_off_of(nxt, x_n);
+        nl2_n = nlse_base[ro];
+        delta_n = a.delta[ro];
+      }
+      // This warpgroup's 72 columns, streamed from tensor memory 16 at a time (the next 16 in flight under
+      // this chunk's exponentials) by a ROLLED loop: the unrolled form is ~20 KB of straight-line code per
+      // unit and had the warps waiting for instruction fetch most of the time.
+      const uint32_t s_row = tmem_s + lane_addr + c0, dp_row = tmem_dp + lane_addr + c0;
+      const uint32_t ds = tmem_ds + (u & 1) * kDqPkColDsStride + lane_addr + wg * (kDqPkHalf / 2);
+      {
+        uint32_t sa[16], pa[16], sb[16], pb[16], s8[8], p8[8];
+        tmem_ld16(s_row, sa);
+        tmem_ld16(dp_row, pa);
+#pragma unroll 1
+        for (int cc = 0; cc < 4; cc += 2) {
+          tmem_wait_ld();
+          tmem_ld16(s_row + (cc + 1) * 16, sb);
+          tmem_ld16(dp_row + (cc + 1) * 16, pb);
+          dqpk_chunk<16>(sa, pa, range_bits(rm.lo - (c0 + cc * 16), rm.hi - (c0 + cc * 16)), scale2, nl22, neg_delta2, acc, ds + cc * 8);
+          tmem_wait_ld();
+          if (cc == 0) {
+            tmem_ld16(s_row + 32, sa);
+            tmem_ld16(dp_row + 32, pa);
+          } else {
+            tmem_ld8(s_row + 64, s8);
+            tmem_ld8(dp_row + 64, p8);
+          }
+          dqpk_chunk<16>(sb, pb, range_bits(rm.lo - (c0 + (cc + 1) * 16), rm.hi - (c0 + (cc + 1) * 16)), scale2, nl22, neg_delta2, acc,
+                         ds + (cc + 1) * 8);
+        }
         tmem_wait_ld();
         tc_fence_before_sync();
-        mbar_arrive(bar_s_free);  // S/dP columns may be overwritten by the next unit
-        uint32_t pk[2][16], pk8[4];
-#pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          // every 32-key chunk is classified for the whole warp: visible to all rows, to none, or mixed
-          const uint32_t bits = range_bits(rm.lo - (c0 + c * 32), rm.hi - (c0 + c * 32));
-          if (__all_sync(0xffffffffu, bits == 0u)) {
-#pragma unroll
-            for (int e = 0; e < 16; ++e) pk[c][e] = 0u;
-          } else if (__all_sync(0xffffffffu, bits == 0xffffffffu)) {
-            dq_compute_chunk<false>(rs[c], rp[c], scale2, nl22, neg_delta2, bits, pk[c], acc);
-          } else {
-            dq_compute_chunk<true>(rs[c], rp[c], scale2, nl22, neg_delta2, bits, pk[c], acc);
-          }
-        }
-        dq_compute_chunk8(rs8, rp8, scale2, nl22, neg_delta2, range_bits(rm.lo - (c0 + 64), rm.hi - (c0 + 64)), pk8, acc);
-        // the dQ MMAs of the previous unit must have left dS (long done: they ran under this unit's exponentials)
-        if (u >= 1 && !(ok = warp_all(mbar_wait(bar_p_free, (u - 1) & 1, abort_flag)))) break;
-        tc_fence_after_sync();
-        const uint32_t ds = tmem_ds + lane_addr + wg * (kDqPkHalf / 2);
-        tmem_st16(ds, pk[0]);
-        tmem_st16(ds + 16, pk[1]);
-        tmem_st4(ds + 32, pk8);
-        tmem_wait_st();
-        tc_fence_before_sync();
-        mbar_arrive(bar_p_full);
-        if (pending) {   // the previous unit's epilogue, its MMAs long retired
-          if (!(ok = epilogue())) break;
-        }
-        pending = true;
-        p_b = cur.b; p_h = cur.g * kPkHeads + hl; p_i = i; p_len = cur.len; p_u = u;
-        p_nl2 = nl2[x];
-        p_pdp = acc.x + acc.y;
+        mbar_arrive(bar_s_free);  // all of S/dP is in registers or used: the next unit's may be computed
+        dqpk_chunk<8>(s8, p8, range_bits(rm.lo - (c0 + 64), rm.hi - (c0 + 64)), scale2, nl22, neg_delta2, acc, ds + 32);
       }
-      if (!ok) break;
+      s_ready = mbar_test_wait(bar_s_full, (u + 1) & 1);   // the next unit's S/dP: asked under the stores
+      tmem_wait_st();
+      tc_fence_before_sync();
+      mbar_arrive(smem_u32(&sm->bar_p_full[u & 1]));
+      // this row's term of the sink gradient for the epilogue warpgroup
+      if (!warp_all(acc_free) && !(ok = warp_all(mbar_wait(bar_out_full, (u - 1) & 1, abort_flag)))) break;
+      sm->acc[wg][r] = (i < len) ? -fast_exp2(sink2 + nl2) * (acc.x + acc.y) : 0.f;
+      mbar_arrive(bar_acc_full);
       cur = nxt;
-      k = k_n;
+      x = x_n;
       have = have_n;
-#pragma unroll
-      for (int x = 0; x < 2; ++x) {
-        nl2[x] = nl2_n[x];
-        delta[x] = delta_n[x];
-      }
+      nl2 = nl2_n;
+      delta = delta_n;
     }
-    if (ok && pending) ok = epilogue();
+    if (!ok && tid == 0) report_abort(a);
   }
   }
 
   tc_fence_before_sync();
   __syncthreads();
-  if (warp == 8) {
+  if (warp == 12) {
     __syncwarp();
     tmem_dealloc(tmem, kDqPkTmemCols);
   }
-  if (sm->abort_flag && tid == 9 * 32) {
+  if (sm->abort_flag && tid == 13 * 32) {
     // abandoned: give copies still in flight a bounded chance to land before shared memory goes away
+    report_abort(a);
     const int issued = sm->loads_issued, q_issued = sm->q_loads_issued;
     for (int uu = max(0, q_issued - 2); uu < q_issued; ++uu) mbar_wait_drain(smem_u32(&sm->bar_q_full[uu & 1]), (uu >> 1) & 1);
     for (int n = max(0, issued - kPkStages); n < issued; ++n)

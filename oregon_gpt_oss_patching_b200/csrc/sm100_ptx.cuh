@@ -98,41 +98,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   return mbar_wait_limit(bar, parity, abort_flag, kWaitLimitCycles);
 }
 
-// try_wait with a suspend-time hint: the hardware may keep the thread suspended for up to `hint_ns` before it
-// reports "not yet", so a role that waits for a long time (an epilogue, a loader) does not spin through the
-// issue slots and the shared-memory pipe the working warps need.
-__device__ __forceinline__ bool mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
-  uint32_t done;
-  asm volatile(
-      "{\n\t"
-      ".reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t"
-      "}\n"
-      : "=r"(done)
-      : "r"(bar), "r"(parity), "r"(hint_ns)
-      : "memory");
-  return done != 0;
-}
-// Bounded wait like mbar_wait, polling through mbar_try_wait_hint.
-__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  long long t0 = 0;
-#pragma unroll 1
-  for (uint32_t it = 1;; ++it) {
-    if (mbar_try_wait_hint(bar, parity, 2000u)) return true;
-    if ((it & 15u) == 0u) {
-      if (*abort_flag) return false;
-      const long long t = clock64();
-      if (t0 == 0) {
-        t0 = t;
-      } else if (t - t0 > kWaitLimitCycles) {
-        *abort_flag = 1;
-        return false;
-      }
-    }
-  }
-}
-
 // Short bounded wait used while abandoning a CTA: lets copies that are still in flight land.
 __device__ __forceinline__ void mbar_wait_drain(uint32_t bar, uint32_t parity) {
   const long long t0 = clock64();
