@@ -278,16 +278,19 @@ int b200attn_bwd_dkdv(const b200attn_params* p) {
   if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kTile))) return rc;
+  CUtensorMap tdk, tdv;   // the tiles leave with one TMA store each
+  if ((rc = make_map(&tdk, p->dk, p->B, p->Hkv, p->S, kTile))) return rc;
+  if ((rc = make_map(&tdv, p->dv, p->B, p->Hkv, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
   const size_t smem = sizeof(DkvSmem) + 1024;
   dim3 grid(a.S_pad / kTile, p->Hkv, p->B);
   if (p->window > 0 && p->window <= 2 * kTile) {
     // narrow window: most tiles are partly masked, skipping the chunks nobody sees pays
     if ((rc = set_smem<attn_bwd_dkdv_kernel<true>>(smem))) return rc;
-    attn_bwd_dkdv_kernel<true><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+    attn_bwd_dkdv_kernel<true><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, tdk, tdv, a);
   } else {
     if ((rc = set_smem<attn_bwd_dkdv_kernel<false>>(smem))) return rc;
-    attn_bwd_dkdv_kernel<false><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, a);
+    attn_bwd_dkdv_kernel<false><<<grid, kDkvThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, tdk, tdv, a);
   }
   return launch_status();
 }

@@ -41,6 +41,7 @@ struct DkvSmem {
   alignas(128) uint8_t side[kDkvStages][kSideTileBytes];  // per item: (-LSE/scale, -delta) of its query rows, 3 bf16 terms each
   alignas(128) uint8_t ones_k[kSideTileBytes];            // ones in the columns of the -LSE/scale terms
   alignas(128) uint8_t ones_v[kSideTileBytes];            // ones in the columns of the -delta terms
+  alignas(1024) uint8_t out[2][kTileBytes];               // dV and dK rows on their way out (TMA store)
   alignas(8) uint64_t bar_kv;                 // K and V landed
   uint64_t bar_in_full[kDkvStages];           // Q, dO and the side tile of a stage landed
   uint64_t bar_in_empty[kDkvStages];          // the dV/dK MMAs reading a stage retired
@@ -115,6 +116,7 @@ template <bool kClassify>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
+                     const __grid_constant__ CUtensorMap tm_dk, const __grid_constant__ CUtensorMap tm_dv,
                      const KernelArgs a) {
   extern __shared__ uint8_t smem_raw[];
   DkvSmem* sm = reinterpret_cast<DkvSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -327,27 +329,39 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       tmem_ld32(src, r0);
       tmem_ld32(src + 32, r1);
       tmem_wait_ld();
-      if (j < a.S) {
-        __nv_bfloat16* dst = wg == 0 ? a.dv.row(b, g, j) : a.dk.row(b, g, j);
+      // The rows leave through shared memory and one TMA store per tensor (issued after the CTA-wide barrier
+      // below): a thread's row is 128 contiguous bytes far from its neighbour's, and as plain stores the two tiles
+      // took 4500 cycles of the load/store unit, a tenth of the CTA's life.  16-byte chunk c of row r goes to
+      // chunk position c ^ (r % 8), the layout the tensor map's 128-byte swizzle expects.
+      uint8_t* const out_row = sm->out[wg] + (tid & 127) * 128;
+      const int rr = tid & 7;
 #pragma unroll
-        for (int c = 0; c < 32; c += 8)
-          store_bf16x8(dst + c, pack_bf16(__uint_as_float(r0[c]) * sc, __uint_as_float(r0[c + 1]) * sc),
-                       pack_bf16(__uint_as_float(r0[c + 2]) * sc, __uint_as_float(r0[c + 3]) * sc),
-                       pack_bf16(__uint_as_float(r0[c + 4]) * sc, __uint_as_float(r0[c + 5]) * sc),
-                       pack_bf16(__uint_as_float(r0[c + 6]) * sc, __uint_as_float(r0[c + 7]) * sc));
-#pragma unroll
-        for (int c = 0; c < 32; c += 8)
-          store_bf16x8(dst + 32 + c, pack_bf16(__uint_as_float(r1[c]) * sc, __uint_as_float(r1[c + 1]) * sc),
-                       pack_bf16(__uint_as_float(r1[c + 2]) * sc, __uint_as_float(r1[c + 3]) * sc),
-                       pack_bf16(__uint_as_float(r1[c + 4]) * sc, __uint_as_float(r1[c + 5]) * sc),
-                       pack_bf16(__uint_as_float(r1[c + 6]) * sc, __uint_as_float(r1[c + 7]) * sc));
+      for (int c = 0; c < 4; ++c) {
+        *reinterpret_cast<uint4*>(out_row + ((c ^ rr) << 4)) =
+            make_uint4(pack_bf16(__uint_as_float(r0[c * 8]) * sc, __uint_as_float(r0[c * 8 + 1]) * sc),
+                       pack_bf16(__uint_as_float(r0[c * 8 + 2]) * sc, __uint_as_float(r0[c * 8 + 3]) * sc),
+                       pack_bf16(__uint_as_float(r0[c * 8 + 4]) * sc, __uint_as_float(r0[c * 8 + 5]) * sc),
+                       pack_bf16(__uint_as_float(r0[c * 8 + 6]) * sc, __uint_as_float(r0[c * 8 + 7]) * sc));
+        *reinterpret_cast<uint4*>(out_row + (((c + 4) ^ rr) << 4)) =
+            make_uint4(pack_bf16(__uint_as_float(r1[c * 8]) * sc, __uint_as_float(r1[c * 8 + 1]) * sc),
+                       pack_bf16(__uint_as_float(r1[c * 8 + 2]) * sc, __uint_as_float(r1[c * 8 + 3]) * sc),
+                       pack_bf16(__uint_as_float(r1[c * 8 + 4]) * sc, __uint_as_float(r1[c * 8 + 5]) * sc),
+                       pack_bf16(__uint_as_float(r1[c * 8 + 6]) * sc, __uint_as_float(r1[c * 8 + 7]) * sc));
       }
+      fence_proxy_async_smem();   // written with ordinary stores, read by the TMA engine
     }
+    if (!ok) sm->abort_flag = 1;   // (already set by whoever gave up; keeps the stores below from running on a partial tile)
   }
   }
 
   tc_fence_before_sync();
   __syncthreads();
+  if (tid == 0 && !sm->abort_flag) {   // rows past the end of the tensor are clipped by the store
+    tma_store_4d(&tm_dv, smem_u32(sm->out[0]), 0, kv0, g, b);
+    tma_store_4d(&tm_dk, smem_u32(sm->out[1]), 0, kv0, g, b);
+    tma_store_commit();
+    tma_store_wait_all();
+  }
   if (warp == 8) {
     __syncwarp();
     tmem_dealloc(tmem, kDkvTmemCols);
