@@ -105,11 +105,15 @@ def main():
     ms = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
     if world > 1:
         torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
+    status = 0
+    if not args.unpatched:
+        from .attention_kernel import last_status
+        status = int(last_status(dev))
     if rank == 0:
         print(json.dumps({
             "metric": "sft_tokens_per_s_per_gpu", "value": round(args.seq / (ms.item() * 1e-3), 1), "unit": "tokens/s/GPU",
             "n_gpus": world, "ms_per_step": round(ms.item(), 1), "steps": args.steps, "warmup": args.warmup,
-            "attention": "hf_eager" if args.unpatched else "b200", "loss": round(float(loss), 4),
+            "attention": "hf_eager" if args.unpatched else "b200", "loss": round(float(loss), 4), "kernel_status": status,
             "config": {"layers": args.layers, "experts": args.experts, "vocab": args.vocab, "seq_len": args.seq,
                        "params_b": round(n_params / 1e9, 2), "batch_per_gpu": 1, "grad_checkpointing": True,
                        "optimizer": "sgd (state-free)", "dp": "replicas + NCCL all-reduce (DDP)" if world > 1 else "none"},
