@@ -171,11 +171,16 @@ def _repeat_kv(x: torch.Tensor, n_rep: int) -> torch.Tensor:
 
 
 def attention_fwd_bwd_dense(q, k, v, sinks, do, scale: float, window: int = 0,
-                            seqlens: Optional[Sequence[int]] = None, dtype=torch.float32):
+                            seqlens: Optional[Sequence[int]] = None, dtype=torch.float32,
+                            cu_seqlens: Optional[Sequence[int]] = None):
     """Eager attention and its autograd gradients on dense (S,S) logits.
 
     Returns ``dict(o, lse, dq, dk, dv, dsinks)``; o is (B,S,Hq,d); lse is the
     log of the softmax denominator including the sink term, (B,Hq,S).
+    With ``cu_seqlens`` (ascending offsets, 0 first, S last) the rows hold documents packed back to
+    back and a token sees only its own document: the causal / sliding-window mask AND-ed with
+    "same document", which is what transformers builds for packed rows
+    (``masking_utils.py``: ``packed_sequence_mask_function`` and-ed into the mask function).
     """
     q = q.detach().to(dtype).requires_grad_(True)
     k = k.detach().to(dtype).requires_grad_(True)
@@ -190,6 +195,10 @@ def attention_fwd_bwd_dense(q, k, v, sinks, do, scale: float, window: int = 0,
         L = None if seqlens is None else int(seqlens[b])
         masks.append(visible_mask(S, window, L, device=q.device))
     vis = torch.stack(masks)[:, None]                                   # (B,1,S,S)
+    if cu_seqlens is not None:
+        ends = torch.as_tensor([int(x) for x in cu_seqlens][1:], device=q.device)
+        doc = torch.bucketize(torch.arange(S, device=q.device), ends, right=True)
+        vis = vis & (doc[:, None] == doc[None, :])
     add_mask = torch.zeros(B, 1, S, S, dtype=dtype, device=q.device).masked_fill(~vis, neg)
 
     ks, vs = _repeat_kv(k, G), _repeat_kv(v, G)                         # :254-255

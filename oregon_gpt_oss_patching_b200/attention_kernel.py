@@ -32,8 +32,8 @@ import torch
 
 from . import _cabi
 
-__all__ = ["attention", "b200_flash_attention", "triton_flash_attention", "seqlens_from_mask", "last_status",
-           "check_status"]
+__all__ = ["attention", "attention_varlen", "b200_flash_attention", "triton_flash_attention", "seqlens_from_mask",
+           "last_status", "check_status"]
 
 _status_words: dict = {}
 
@@ -203,6 +203,91 @@ def _maybe_check_status(device) -> None:
 attention = _attention.apply
 
 
+def _doc_bounds(cu_seqlens, total: int) -> list:
+    """Document boundaries as a validated list of Python ints (a device tensor is read back once)."""
+    bounds = [int(x) for x in (cu_seqlens.tolist() if isinstance(cu_seqlens, torch.Tensor) else cu_seqlens)]
+    if len(bounds) < 2 or bounds[0] != 0 or bounds[-1] != total or any(b1 < b0 for b0, b1 in zip(bounds, bounds[1:])):
+        raise ValueError(f"cu_seqlens must rise from 0 to the packed length {total}, got {bounds}")
+    return bounds
+
+
+class _attention_varlen(torch.autograd.Function):
+    """forward(q, k, v, sinks, sm_scale, bandwidth, cu_seqlens) -> o (1,T,Hq,d) for packed documents.
+
+    q (1,Hq,T,d) and k, v (1,Hkv,T,d) hold several documents back to back along the position axis;
+    ``cu_seqlens`` (n_docs+1 ascending offsets, 0 first and T last: the convention of the varlen
+    flash-attention interfaces HF passes as ``cu_seq_lens_q``) says where each starts.  A token attends
+    only inside its own document (causal, sliding window and sink as in ``attention``).  The reference
+    has no such entry (it ignores masks and position ids, ``attention_kernel.py:353-358``, so packed
+    documents attend to each other there).
+
+    Every document is one call of the same kernels on views of the packed tensors -- a document's rows
+    are contiguous along the position axis whatever the outer strides, and the tensor maps of a call
+    end at the document's last row, so loads past it read zeros and stores are clipped; nothing is
+    copied or padded.  dSinks is the sum of the documents' contributions, added in document order.
+    """
+
+    @staticmethod
+    def forward(ctx, q, k, v, sinks, sm_scale, bandwidth, cu_seqlens):
+        _check_inputs(q, k, v, sinks)
+        if q.shape[0] != 1:
+            raise ValueError("packed documents come as one row: q (1,Hq,T,d), k/v (1,Hkv,T,d)")
+        lib = _cabi.load()
+        q, k, v = _as_view(q), _as_view(k), _as_view(v)
+        _, Hq, T, d = q.shape
+        bounds = _doc_bounds(cu_seqlens, T)
+        window = int(bandwidth) if bandwidth else 0
+        o = torch.empty((1, T, Hq, d), dtype=q.dtype, device=q.device)
+        docs = [(a, b) for a, b in zip(bounds, bounds[1:]) if b > a]
+        pads = [_cabi.padded_len(b - a) for a, b in docs]
+        lse = torch.empty((Hq * sum(pads),), dtype=torch.float32, device=q.device)
+        sinks_f32 = sinks.detach().to(torch.float32).contiguous()
+        off = 0
+        for (a, b), pad in zip(docs, pads):
+            p = _params(q[:, :, a:b], k[:, :, a:b], v[:, :, a:b], o[:, a:b], lse[off:off + Hq * pad], sinks_f32,
+                        sm_scale, window, None)
+            _cabi.check(lib.b200attn_fwd(ctypes.byref(p)), "b200attn_fwd")
+            off += Hq * pad
+        ctx.save_for_backward(q, k, v, sinks, o, lse)
+        ctx.sm_scale, ctx.window, ctx.docs, ctx.pads = float(sm_scale), window, docs, pads
+        _maybe_check_status(q.device)
+        return o
+
+    @staticmethod
+    def backward(ctx, do):
+        q, k, v, sinks, o, lse = ctx.saved_tensors
+        lib = _cabi.load()
+        do = _as_view(do if do.dtype == q.dtype else do.to(q.dtype))
+        _, Hq, T, d = q.shape
+        Hkv = k.shape[1]
+        dq = torch.empty((1, Hq, T, d), dtype=q.dtype, device=q.device)
+        dk = torch.empty((1, Hkv, T, d), dtype=k.dtype, device=q.device)
+        dv = torch.empty((1, Hkv, T, d), dtype=v.dtype, device=q.device)
+        sinks_f32 = sinks.detach().to(torch.float32).contiguous()
+        dsinks = torch.zeros((max(len(ctx.docs), 1), Hq), dtype=torch.float32, device=q.device)
+        delta = torch.empty((_cabi.DELTA_PLANES * Hq * max(ctx.pads, default=0),), dtype=torch.float32, device=q.device)
+        partial = None
+        off = 0
+        for i, ((a, b), pad) in enumerate(zip(ctx.docs, ctx.pads)):
+            p = _params(q[:, :, a:b], k[:, :, a:b], v[:, :, a:b], o[:, a:b], lse[off:off + Hq * pad], sinks_f32,
+                        ctx.sm_scale, ctx.window, None)
+            p.d_o = _cabi.tensor4(do[:, a:b], "bshd")
+            p.dq, p.dk, p.dv = (_cabi.tensor4(t[:, :, a:b], "bhsd") for t in (dq, dk, dv))
+            p.delta = delta.data_ptr()          # scratch of one document at a time: calls run in stream order
+            p.dsinks = dsinks[i].data_ptr()
+            need = int(lib.b200attn_dsinks_scratch_floats(ctypes.byref(p)))
+            if partial is None or partial.numel() < need:
+                partial = torch.empty((need,), dtype=torch.float32, device=q.device)
+            p.dsinks_partial = partial.data_ptr()
+            _cabi.check(lib.b200attn_bwd(ctypes.byref(p)), "b200attn_bwd")
+            off += Hq * pad
+        _maybe_check_status(q.device)
+        return dq, dk, dv, dsinks.sum(dim=0).to(sinks.dtype), None, None, None
+
+
+attention_varlen = _attention_varlen.apply
+
+
 def b200_flash_attention(
     module,
     query: torch.Tensor,
@@ -217,10 +302,14 @@ def b200_flash_attention(
 
     Reads ``module.sinks`` and ``module.sliding_window`` like the reference adapter
     (``attention_kernel.py:348-358``); ``dropout`` and the extra keyword arguments HF passes
-    (``sliding_window``, ``s_aux``, ``position_ids`` ...) are ignored as they are there.
+    (``sliding_window``, ``s_aux``, ``position_ids`` ...) are ignored as they are there, except
+    ``cu_seq_lens_q``: with batch 1 and more than one document it selects ``attention_varlen``.
     Returns ``(attn_output (B,S,Hq,d), None)``.
     """
     B, _, S, _ = query.shape
+    cu = kwargs.get("cu_seq_lens_q")
+    if cu is not None and B == 1 and len(cu) > 2:       # HF's padding-free collation: documents packed in one row
+        return attention_varlen(query, key, value, module.sinks, scaling, module.sliding_window, cu), None
     seqlens = seqlens_from_mask(attention_mask, B, S)
     return attention(query, key, value, module.sinks, scaling, module.sliding_window, seqlens), None
 

@@ -113,3 +113,22 @@ def test_work_counts_match_the_published_table():
     assert abs(algorithmic_flops(CONFIGS["cfg2"])["total"] / 1.9246e12 - 1) < 1e-3
     assert abs(algorithmic_bytes(CONFIGS["cfg3"])["total"] / 1829e6 - 1) < 2e-3
     assert CONFIGS["cfg4_swa"].seqlens == (14090, 10808, 8875, 5168, 5752, 1653, 2179, 1277)
+
+
+@pytest.mark.parametrize("window", [0, 16])
+def test_packed_documents_equal_the_documents_taken_one_by_one(window):
+    """The same-document mask of the dense oracle == running every document alone (dSinks adds up)."""
+    bounds = [0, 1, 40, 40, 97, 128]
+    case = AttnCase("t", B=1, S=bounds[-1], Hq=4, Hkv=2, window=window, seed=21)
+    q, k, v, do, sinks = make_inputs(case)
+    packed = attention_fwd_bwd_dense(q, k, v, sinks, do, case.scale, window, cu_seqlens=bounds)
+    dsinks = torch.zeros_like(packed["dsinks"])
+    for a, b in zip(bounds, bounds[1:]):
+        if b == a:
+            continue
+        one = attention_fwd_bwd_dense(q[:, :, a:b], k[:, :, a:b], v[:, :, a:b], sinks, do[:, a:b], case.scale, window)
+        assert rel_err(packed["o"][:, a:b], one["o"]) < TOL and rel_err(packed["lse"][:, :, a:b], one["lse"]) < TOL
+        for key in ("dq", "dk", "dv"):
+            assert rel_err(packed[key][:, :, a:b], one[key]) < TOL, key
+        dsinks += one["dsinks"]
+    assert rel_err(packed["dsinks"], dsinks) < TOL
