@@ -130,6 +130,9 @@ def kernel_work(case, algorithmic_flops, algorithmic_bytes):
         "bwd_dsinks": {"flops": 0, "bytes": row // 32 + 4 * case.Hq},
         "bwd_dkdv": {"flops": 8 * unit, "bytes": 2 * qb + 2 * kb + 2 * row + 2 * kb},
         "bwd_dq": {"flops": 6 * unit, "bytes": 2 * qb + 2 * kb + 2 * row + qb},
+        # narrow windows: one kernel makes dK, dV and dQ (S, dP once), after a preprocess that also clears dQ
+        "bwd_preprocess_fused": {"flops": 0, "bytes": 2 * qb + 2 * row + qb},
+        "bwd_fused": {"flops": 10 * unit, "bytes": 2 * qb + 2 * kb + 2 * row + 2 * kb + qb},
     }
 
 
@@ -211,10 +214,15 @@ def run_b200(args, rank, world, local_rank):
     stream = torch.cuda.current_stream(dev)
     p, keep = resident_problem(lib, qd, kd, vd, dod, sinks, seqlens, case.scale, case.window, local_rank, stream)
     status = keep["status"]
-    stages = [("fwd", lib.b200attn_fwd), ("bwd_preprocess", lib.b200attn_bwd_preprocess),
-              ("bwd_dkdv", lib.b200attn_bwd_dkdv), ("bwd_dq", lib.b200attn_bwd_dq),
-              ("bwd_dsinks", lib.b200attn_bwd_dsinks)]
     pref = ctypes.byref(p)
+    if lib.b200attn_bwd_dq_is_fused(pref):
+        # window <= 128: the dkdv stage is the one backward kernel (dK, dV and dQ); the dq stage would return at once
+        stages = [("fwd", lib.b200attn_fwd), ("bwd_preprocess_fused", lib.b200attn_bwd_preprocess),
+                  ("bwd_fused", lib.b200attn_bwd_dkdv), ("bwd_dsinks", lib.b200attn_bwd_dsinks)]
+    else:
+        stages = [("fwd", lib.b200attn_fwd), ("bwd_preprocess", lib.b200attn_bwd_preprocess),
+                  ("bwd_dkdv", lib.b200attn_bwd_dkdv), ("bwd_dq", lib.b200attn_bwd_dq),
+                  ("bwd_dsinks", lib.b200attn_bwd_dsinks)]
 
     def step_resident(events=None):
         for idx, (name, fn) in enumerate(stages):

@@ -41,7 +41,7 @@ extern "C" {
 
 #define B200ATTN_VERSION 1
 #define B200ATTN_ROW_TILE 128 /* lse/delta rows are padded to a multiple of this */
-#define B200ATTN_DELTA_PLANES 10 /* the delta scratch holds this many fp32-sized values per (b, h, padded row) */
+#define B200ATTN_DELTA_PLANES 6 /* the delta scratch holds this many fp32-sized values per (b, h, padded row) */
 
 enum {
   B200ATTN_OK = 0,
@@ -97,7 +97,8 @@ typedef struct b200attn_params {
   b200attn_tensor d_o;        /* gradient of o */
   b200attn_tensor dq, dk, dv; /* outputs, fully overwritten (no pre-zeroing needed) */
   float* delta;               /* (B200ATTN_DELTA_PLANES,B,Hq,S_pad) fp32-sized scratch: [0] rowsum(dO*O),
-                                 [1] -lse*log2(e), [2..9] MMA side operands of the dK/dV kernel (bf16) */
+                                 [1] -lse*log2(e) (the sink's probability per row where b200attn_bwd_dq_is_fused()),
+                                 [2..5] MMA side operands of the dK/dV kernels (bf16) */
   float* dsinks;              /* (Hq) fp32 output, overwritten */
   float* dsinks_partial;      /* fp32 scratch of b200attn_dsinks_scratch_floats() elements */
 } b200attn_params;
@@ -132,9 +133,18 @@ int b200attn_fwd(const b200attn_params* p);
  */
 int b200attn_bwd(const b200attn_params* p);
 
-/* Backward stages, exported separately so that each can be timed and tested alone. */
+/* Backward stages, exported separately so that each can be timed and tested alone.
+ *
+ * Layers with a sliding window of at most 128 keys (b200attn_bwd_dq_is_fused() == 1) have a shorter
+ * backward: a query tile is seen by at most two key tiles there, so ONE kernel computes dK, dV and dQ
+ * (S, dP and the exponentials once instead of twice) and adds its bf16 dQ tiles into global memory --
+ * two terms per element, so the sum does not depend on their order and the result stays
+ * bit-reproducible.  For such layers the preprocess stage also clears dq and writes the sink-gradient
+ * partials (it needs dq and dsinks_partial), the dkdv stage runs that kernel (it needs dq, which must
+ * still hold the zeros of the preprocess stage), and the dq stage returns at once. */
+int b200attn_bwd_dq_is_fused(const b200attn_params* p);
 
-/* delta[0] = rowsum(dO * O), delta[1] = -lse * log2(e), delta[2..9] = the same two per-row constants
+/* delta[0] = rowsum(dO * O), delta[1] = -lse * log2(e), delta[2..5] = the same two per-row constants
  * as bf16 MMA operand tiles for the dK/dV kernel.  Replaces `_attn_bwd_precompute_D`
  * (attention_kernel.py:102-120).  Reads o, dO, lse; writes delta. */
 int b200attn_bwd_preprocess(const b200attn_params* p);
@@ -163,7 +173,7 @@ int b200attn_bwd_dq(const b200attn_params* p);
  * implicit synchronisation) is not acceptable, and bindings from runtimes that own the
  * allocator and do not let foreign code use it.  For them the two scratch buffers of
  * b200attn_bwd (`delta` and `dsinks_partial`, which are ignored here and may be NULL) live in
- * a fixed array inside the library's device image: about 10.6 MB that every GPU loading the
+ * a fixed array inside the library's device image: about 6.4 MB that every GPU loading the
  * library holds until the process exits.  Inputs and outputs are still the caller's.
  *
  *   - Limit: B * Hq * b200attn_padded_len(S) <= B200ATTN_STATIC_MAX_ROWS (e.g. B=1, Hq=64,

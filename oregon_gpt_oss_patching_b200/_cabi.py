@@ -11,12 +11,13 @@ import threading
 
 from . import build as _build
 
-DELTA_PLANES = 10   # B200ATTN_DELTA_PLANES of include/b200attn.h: fp32-sized values per (b, h, padded row) in the delta scratch
+DELTA_PLANES = 6   # B200ATTN_DELTA_PLANES of include/b200attn.h: fp32-sized values per (b, h, padded row) in the delta scratch
 
 EXPORTS = (
     "b200attn_version", "b200attn_sizeof_params", "b200attn_strerror", "b200attn_padded_len", "b200attn_dsinks_scratch_floats",
     "b200attn_fwd", "b200attn_bwd", "b200attn_bwd_preprocess", "b200attn_bwd_dsinks", "b200attn_bwd_dkdv",
-    "b200attn_bwd_dq", "b200attn_bwd_static_scratch", "b200attn_umma_selftest", "b200attn_wait_selftest",
+    "b200attn_bwd_dq", "b200attn_bwd_dq_is_fused", "b200attn_bwd_static_scratch", "b200attn_umma_selftest",
+    "b200attn_wait_selftest",
 )
 
 ROW_TILE = 128
@@ -79,7 +80,7 @@ def load() -> ctypes.CDLL:
         lib.b200attn_dsinks_scratch_floats.restype = ctypes.c_int64
         lib.b200attn_dsinks_scratch_floats.argtypes = [pp]
         for name in ("b200attn_fwd", "b200attn_bwd", "b200attn_bwd_preprocess", "b200attn_bwd_dsinks",
-                     "b200attn_bwd_dkdv", "b200attn_bwd_dq", "b200attn_bwd_static_scratch"):
+                     "b200attn_bwd_dkdv", "b200attn_bwd_dq", "b200attn_bwd_dq_is_fused", "b200attn_bwd_static_scratch"):
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int
             fn.argtypes = [pp]

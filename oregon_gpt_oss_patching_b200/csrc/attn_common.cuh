@@ -38,7 +38,9 @@ struct KernelArgs {
   float* delta;                     // (B,Hq,S_pad)
   float* dsinks;                    // (Hq)
   float* dsinks_partial;            // (Hq, B * S_pad/128 * partials_per_tile)
-  int partials_per_tile;            // sink-gradient partials the dQ kernel in use writes per (head, 128 positions)
+  int partials_per_tile;            // sink-gradient partials written per (head, 128 positions) by the kernel that makes them
+  int fused_bwd;                    // 1: narrow window, one kernel makes dK, dV and dQ; the preprocess kernel clears dQ
+                                    //    and writes the sink-gradient partials
   StridedPtr o, d_o, dq, dk, dv;    // tensors touched with plain loads/stores
   StridedPtr q, k, v;
 };
@@ -91,11 +93,23 @@ __device__ __forceinline__ uint64_t desc_kmajor(uint32_t smem_addr) {
 __device__ __forceinline__ uint64_t desc_mnmajor(uint32_t smem_addr) {
   return make_smem_desc_sw128(smem_addr, kTileBytes, 1024);
 }
-// A (rows x 16) bf16 side operand, K-contiguous, unswizzled: core matrix (row group rg, 8-column
-// half kc) at byte rg*256 + kc*128, element (r, c) at + (r%8)*16 + (c%8)*2.  One k-step of an MMA.
-constexpr int kSideTileBytes = kTile * 16 * 2;   // 4 KB
-__device__ __forceinline__ uint64_t desc_side(uint32_t smem_addr) { return make_smem_desc_noswizzle(smem_addr, 128, 256); }
-__device__ __forceinline__ uint32_t side_offset(int row, int half) { return (row >> 3) * 256 + half * 128 + (row & 7) * 16; }
+// The (rows x 16) bf16 operands of the extra k-step, K-contiguous, unswizzled, made of 8-row x 16-byte core
+// matrices (128 contiguous bytes each).
+//   "ones" tiles (A operand, constant): core matrix (row group rg, 8-column half kc) at rg*256 + kc*128,
+//   element (r, c) at + (r%8)*16 + (c%8)*2; the second half (columns 8-15) is all zeros.
+//   side tiles (B operand, from the preprocess kernel): only columns 0-7 exist, 16 bytes per row: row group rg
+//   at rg*128.  The descriptor's K-neighbour offset equals the row-group offset, so the "second half" of a row
+//   group reads the next row group's real (finite) values -- times the zeros of the A operand's second half.
+//   The last row group reads 128 bytes past the tile: every shared-memory copy is followed by a 128-byte pad
+//   that the kernel zeroes once.
+constexpr int kOnesTileBytes = kTile * 16 * 2;   // 4 KB
+constexpr int kSideTileBytes = kTile * 8 * 2;    // 2 KB: 16 bytes per query row
+constexpr int kSidePadBytes = 128;
+constexpr int kSideRowBytes = 16;
+__device__ __forceinline__ uint64_t desc_ones(uint32_t smem_addr) { return make_smem_desc_noswizzle(smem_addr, 128, 256); }
+__device__ __forceinline__ uint64_t desc_side(uint32_t smem_addr) { return make_smem_desc_noswizzle(smem_addr, 128, 128); }
+__device__ __forceinline__ uint32_t ones_offset(int row, int half) { return (row >> 3) * 256 + half * 128 + (row & 7) * 16; }
+__device__ __forceinline__ uint32_t side_offset(int row) { return (row >> 3) * 128 + (row & 7) * 16; }
 constexpr uint32_t kDescKStepKMajor = 32 >> 4;     // +32 B per K-step, in 16-byte units
 constexpr uint32_t kDescKStepMNMajor = 2048 >> 4;  // +2048 B per K-step
 

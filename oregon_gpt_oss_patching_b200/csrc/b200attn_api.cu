@@ -11,9 +11,9 @@
 #include "attn_common.cuh"
 #include "bwd_dkdv_kernel.cuh"
 #include "bwd_dq_kernel.cuh"
-#include "bwd_dq_packed_kernel.cuh"
 #include "bwd_dq_persistent_kernel.cuh"
 #include "bwd_preprocess_kernel.cuh"
+#include "bwd_window_fused_kernel.cuh"
 #include "fwd_kernel.cuh"
 #include "fwd_packed_kernel.cuh"
 #include "umma_selftest.cuh"
@@ -125,6 +125,7 @@ int validate(const b200attn_params* p, int need) {
 }
 
 bool packed_window_layer(const b200attn_params* p);
+bool fused_window_bwd(const b200attn_params* p);
 
 KernelArgs make_args(const b200attn_params* p) {
   KernelArgs a{};
@@ -141,7 +142,8 @@ KernelArgs make_args(const b200attn_params* p) {
   a.delta = p->delta;
   a.dsinks = p->dsinks;
   a.dsinks_partial = p->dsinks_partial;
-  a.partials_per_tile = packed_window_layer(p) ? kDqPkPartialsPerTile : 8;
+  a.fused_bwd = fused_window_bwd(p) ? 1 : 0;
+  a.partials_per_tile = a.fused_bwd ? kFwSinkPartials : 8;
   a.o = strided(p->o); a.d_o = strided(p->d_o); a.dq = strided(p->dq); a.dk = strided(p->dk); a.dv = strided(p->dv);
   a.q = strided(p->q); a.k = strided(p->k); a.v = strided(p->v);
   return a;
@@ -167,6 +169,10 @@ int set_smem(size_t bytes) {
 bool packed_window_layer(const b200attn_params* p) {
   return p->window > 0 && p->window <= kPkMaxWindow && p->Hq / p->Hkv == kPkHeads;
 }
+
+// Layers whose backward is one kernel: a query tile is seen by at most two key tiles, so the kernel's dQ
+// contributions can be added in global memory without the result depending on their order.
+bool fused_window_bwd(const b200attn_params* p) { return p->window > 0 && p->window <= kFwMaxWindow; }
 
 int launch_status() { return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ECUDA; }
 
@@ -198,7 +204,7 @@ int64_t b200attn_padded_len(int64_t S) { return (S + B200ATTN_ROW_TILE - 1) / B2
 
 int64_t b200attn_dsinks_scratch_floats(const b200attn_params* p) {
   if (p == nullptr) return 0;
-  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 8;
+  return (int64_t)p->Hq * p->B * (b200attn_padded_len(p->S) / B200ATTN_ROW_TILE) * 9;
 }
 
 int b200attn_fwd(const b200attn_params* p) {
@@ -247,8 +253,11 @@ int b200attn_fwd(const b200attn_params* p) {
   return launch_status();
 }
 
+int b200attn_bwd_dq_is_fused(const b200attn_params* p) { return (p != nullptr && fused_window_bwd(p)) ? 1 : 0; }
+
 int b200attn_bwd_preprocess(const b200attn_params* p) {
-  int rc = validate(p, kNeedBwdIn | kNeedDelta);
+  if (p == nullptr) return B200ATTN_EINVAL;
+  int rc = validate(p, kNeedBwdIn | kNeedDelta | (fused_window_bwd(p) ? (kNeedDq | kNeedPartial) : 0));
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
@@ -269,7 +278,8 @@ int b200attn_bwd_dsinks(const b200attn_params* p) {
 }
 
 int b200attn_bwd_dkdv(const b200attn_params* p) {
-  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedDkv);
+  if (p == nullptr) return B200ATTN_EINVAL;
+  int rc = validate(p, kNeedBwdIn | kNeedDelta | kNeedDkv | (fused_window_bwd(p) ? kNeedDq : 0));
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
@@ -282,8 +292,17 @@ int b200attn_bwd_dkdv(const b200attn_params* p) {
   if ((rc = make_map(&tdk, p->dk, p->B, p->Hkv, p->S, kTile))) return rc;
   if ((rc = make_map(&tdv, p->dv, p->B, p->Hkv, p->S, kTile))) return rc;
   const KernelArgs a = make_args(p);
-  const size_t smem = sizeof(DkvSmem) + 1024;
   dim3 grid(a.S_pad / kTile, p->Hkv, p->B);
+  if (fused_window_bwd(p)) {
+    // narrow window: dQ comes out of the same pass (added into the rows the preprocess kernel cleared)
+    CUtensorMap tdq;
+    if ((rc = make_map(&tdq, p->dq, p->B, p->Hq, p->S, kTile))) return rc;
+    const size_t fsmem = sizeof(FwSmem) + 1024;
+    if ((rc = set_smem<attn_bwd_window_fused_kernel>(fsmem))) return rc;
+    attn_bwd_window_fused_kernel<<<grid, kFwThreads, fsmem, static_cast<cudaStream_t>(p->stream)>>>(tq, tk, tv, tdo, tdk, tdv, tdq, a);
+    return launch_status();
+  }
+  const size_t smem = sizeof(DkvSmem) + 1024;
   if (p->window > 0 && p->window <= 2 * kTile) {
     // narrow window: most tiles are partly masked, skipping the chunks nobody sees pays
     if ((rc = set_smem<attn_bwd_dkdv_kernel<true>>(smem))) return rc;
@@ -300,25 +319,9 @@ int b200attn_bwd_dq(const b200attn_params* p) {
   if (rc) return rc;
   DeviceGuard guard(p->device);
   if (!guard.ok) return B200ATTN_ECUDA;
+  if (fused_window_bwd(p)) return B200ATTN_OK;   // the dK/dV stage made dQ as well
   CUtensorMap tk, tv;
   const KernelArgs a = make_args(p);
-  if (packed_window_layer(p)) {
-    // the GPT-OSS sliding-window layer: tiles of 8 heads x 16 positions, one 144-key product per tile
-    CUtensorMap tq, tdo, tdq;
-    if ((rc = make_map(&tq, p->q, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
-    if ((rc = make_map(&tdo, p->d_o, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
-    if ((rc = make_map(&tdq, p->dq, p->B, p->Hq, p->S, kPkPos, kPkHeads))) return rc;
-    if ((rc = make_map(&tk, p->k, p->B, p->Hkv, p->S, kPkKvRows))) return rc;
-    if ((rc = make_map(&tv, p->v, p->B, p->Hkv, p->S, kPkKvRows))) return rc;
-    const size_t smem = sizeof(DqPkSmem) + 1024;
-    if ((rc = set_smem<attn_bwd_dq_packed_kernel>(smem))) return rc;
-    int n_sm = 0;
-    if (cudaDeviceGetAttribute(&n_sm, cudaDevAttrMultiProcessorCount, p->device) != cudaSuccess || n_sm <= 0) return B200ATTN_ECUDA;
-    const long long n_items = (long long)(a.S_pad / kPkItemPos) * p->B * p->Hkv;
-    const unsigned pgrid = (unsigned)(n_items < n_sm ? n_items : n_sm);
-    attn_bwd_dq_packed_kernel<<<pgrid, kDqPkThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(tq, tdo, tk, tv, tdq, a);
-    return launch_status();
-  }
   dim3 grid(a.S_pad / kTile, p->Hq, p->B);
   if (p->window > 0 && p->window <= 8 * kTile) {
     // short work items (at most nine key tiles per query tile; measured cross-over between 1024 and 2048
@@ -356,10 +359,10 @@ int b200attn_bwd(const b200attn_params* p) {
 
 // ---- backward without caller-provided scratch ------------------------------------------------
 // Fixed device-resident scratch for b200attn_bwd_static_scratch.  Every GPU that loads the
-// library holds these ~10.6 MB until the process exits.
+// library holds these ~6.4 MB until the process exits.
 constexpr int64_t kStaticMaxRows = B200ATTN_STATIC_MAX_ROWS;
 static __device__ __align__(256) float g_static_delta[B200ATTN_DELTA_PLANES * kStaticMaxRows];   // delta | -lse*log2(e) | side tiles
-static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 16];  // 8 partials per 128 rows
+static __device__ __align__(256) float g_static_dsinks_partial[kStaticMaxRows / 128 * 9];  // up to 9 partials per 128 rows
 
 namespace {
 std::mutex g_static_mutex;

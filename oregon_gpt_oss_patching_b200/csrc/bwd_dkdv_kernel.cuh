@@ -38,9 +38,9 @@ struct DkvSmem {
   alignas(1024) uint8_t v[kTileBytes];
   alignas(1024) uint8_t q[kDkvStages][kTileBytes];
   alignas(1024) uint8_t d_o[kDkvStages][kTileBytes];
-  alignas(128) uint8_t side[kDkvStages][kSideTileBytes];  // per item: (-LSE/scale, -delta) of its query rows, 3 bf16 terms each
-  alignas(128) uint8_t ones_k[kSideTileBytes];            // ones in the columns of the -LSE/scale terms
-  alignas(128) uint8_t ones_v[kSideTileBytes];            // ones in the columns of the -delta terms
+  alignas(128) uint8_t side[kDkvStages][kSideTileBytes + kSidePadBytes];  // per item: (-LSE/scale, -delta) of its query rows, 3 bf16 terms each
+  alignas(128) uint8_t ones_k[kOnesTileBytes];            // ones in the columns of the -LSE/scale terms
+  alignas(128) uint8_t ones_v[kOnesTileBytes];            // ones in the columns of the -delta terms
   alignas(1024) uint8_t out[2][kTileBytes];               // dV and dK rows on their way out (TMA store)
   alignas(8) uint64_t bar_kv;                 // K and V landed
   uint64_t bar_in_full[kDkvStages];           // Q, dO and the side tile of a stage landed
@@ -143,7 +143,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   const int qt_first = kt;
   const int nq = i_max / kTile - qt_first + 1;  // query tiles per head
   const int n_items = nq * a.group;
-  // side tiles of the preprocess kernel: planes 2.. of the delta scratch, 32 bytes per query row
+  // side tiles of the preprocess kernel: planes 2..5 of the delta scratch, 16 bytes per query row
   const uint8_t* side_base = reinterpret_cast<const uint8_t*>(a.delta + 2ll * a.B * a.Hq * a.S_pad);
 
   const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_acc = smem_u32(&sm->bar_acc), bar_s_full = smem_u32(&sm->bar_s_full),
@@ -169,10 +169,12 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
   if (tid < kTile) {
     // constant A operands of the extra k-step: ones in columns 0-2 resp. 4-6 of row `tid`
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    *reinterpret_cast<uint4*>(sm->ones_k + side_offset(tid, 0)) = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
-    *reinterpret_cast<uint4*>(sm->ones_v + side_offset(tid, 0)) = make_uint4(0u, 0u, 0x3f803f80u, 0x00003f80u);
-    *reinterpret_cast<uint4*>(sm->ones_k + side_offset(tid, 1)) = zero;
-    *reinterpret_cast<uint4*>(sm->ones_v + side_offset(tid, 1)) = zero;
+    *reinterpret_cast<uint4*>(sm->ones_k + ones_offset(tid, 0)) = make_uint4(0x3f803f80u, 0x00003f80u, 0u, 0u);
+    *reinterpret_cast<uint4*>(sm->ones_v + ones_offset(tid, 0)) = make_uint4(0u, 0u, 0x3f803f80u, 0x00003f80u);
+    *reinterpret_cast<uint4*>(sm->ones_k + ones_offset(tid, 1)) = zero;
+    *reinterpret_cast<uint4*>(sm->ones_v + ones_offset(tid, 1)) = zero;
+    if (tid < kDkvStages * (kSidePadBytes / 16))   // the pads behind the side tiles: read as the last row group's second half
+      *reinterpret_cast<uint4*>(sm->side[tid / (kSidePadBytes / 16)] + kSideTileBytes + (tid % (kSidePadBytes / 16)) * 16) = zero;
     fence_proxy_async_smem();   // written with ordinary stores, read by the tensor core
   }
   if (warp == 8) {
@@ -214,7 +216,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
         mbar_arrive_expect_tx(bar, kDkvStageBytes);
         tma_load_4d(smem_u32(sm->q[s]), &tm_q, bar, 0, item_q0, h, b);
         tma_load_4d(smem_u32(sm->d_o[s]), &tm_do, bar, 0, item_q0, h, b);
-        bulk_load_1d(smem_u32(sm->side[s]), side_base + row_off * 32, kSideTileBytes, bar);
+        bulk_load_1d(smem_u32(sm->side[s]), side_base + row_off * kSideRowBytes, kSideTileBytes, bar);
         *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
         if (++qi == nq) {
           qi = 0;
@@ -232,7 +234,7 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       const uint32_t idesc_front = make_idesc_bf16(kTile, kTile, 0, 0);    // A, B both K-contiguous, N = 128
       const uint64_t k_desc = desc_kmajor(smem_u32(sm->k));
       const uint64_t v_desc = desc_kmajor(smem_u32(sm->v));
-      const uint64_t ones_k_desc = desc_side(smem_u32(sm->ones_k)), ones_v_desc = desc_side(smem_u32(sm->ones_v));
+      const uint64_t ones_k_desc = desc_ones(smem_u32(sm->ones_k)), ones_v_desc = desc_ones(smem_u32(sm->ones_v));
       bool ok = mbar_wait(bar_kv, 0, abort_flag);
       for (int it = 0; ok && it < n_items; ++it) {
         // the stage has landed and the previous item's S^T/dP^T are in registers

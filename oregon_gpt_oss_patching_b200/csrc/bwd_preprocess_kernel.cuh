@@ -3,12 +3,18 @@
 // attn_bwd_preprocess_kernel:  delta[b,h,i] = sum_c dO[b,h,i,c] * O[b,h,i,c]  in fp32 (the
 // reference's `_attn_bwd_precompute_D`, attention_kernel.py:102-120); the second half of the
 // scratch receives -LSE*log2(e), the exponent offset the dQ kernels add per query row, and planes
-// 2.. the dK/dV kernel's side tiles: per 128 query rows a (128 x 16) bf16 MMA operand in the
-// unswizzled core-matrix layout (see side_offset) whose row i holds -LSE_i/scale in columns 0-2 and
-// -delta_i in columns 4-6, each as three bf16 terms (hi, mid, lo: 24 mantissa bits), zeros elsewhere.
+// 2..5 the dK/dV kernel's side tiles: per 128 query rows the first eight columns of a (128 x 16) bf16
+// MMA operand in the unswizzled core-matrix layout (see side_offset), 16 bytes per row: row i holds
+// -LSE_i/scale in columns 0-2 and -delta_i in columns 4-6, each as three bf16 terms (hi, mid, lo: 24
+// mantissa bits).
 //
-// attn_bwd_dsinks_kernel:  dsinks[h] = sum of head h's per-warp partials written by the dQ
-// kernel, in a fixed order with a warp-shuffle tree, so the result is bit-reproducible (the
+// With a.fused_bwd (narrow windows, where one kernel makes dK, dV and dQ and adds its dQ tiles into
+// global memory) the kernel also clears its 128 rows of dQ, leaves w_i = 2^(sink_h*log2e - LSE_i*log2e)
+// (the sink's probability in row i; 0 for padding rows) in the second plane instead of -LSE*log2(e), and
+// writes its part of the sink gradient, -sum_i w_i (1 - w_i) delta_i (the backward kernel adds the rest).
+//
+// attn_bwd_dsinks_kernel:  dsinks[h] = sum of head h's partials written by the dQ kernel (or, see
+// above, by the preprocess kernel), in a fixed order with a warp-shuffle tree, so the result is bit-reproducible (the
 // reference adds its per-tile terms with relaxed atomics, attention_kernel.py:176).
 #pragma once
 #include "attn_common.cuh"
@@ -49,12 +55,20 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
   const int part = lane & 7;       // 16-byte slice of the row
   const long long row_base = ((long long)(b * a.Hq + h)) * a.S_pad + (long long)tile * kTile;
   const long long nlse_off = (long long)a.B * a.Hq * a.S_pad;  // plane 1 of the scratch: -LSE*log2(e)
-  uint8_t* side_base = reinterpret_cast<uint8_t*>(a.delta + 2 * nlse_off);   // planes 2..: side tiles, 32 bytes per row
+  uint8_t* side_base = reinterpret_cast<uint8_t*>(a.delta + 2 * nlse_off);   // planes 2..5: side tiles, 16 bytes per row
   const float inv_scale = 1.f / a.scale;
 
   // the CTA's side tile is put together in shared memory and leaves with coalesced 16-byte stores
   __shared__ uint4 side_tile[kSideTileBytes / 16];
-  side_tile[side_offset(tid, 1) >> 4] = make_uint4(0u, 0u, 0u, 0u);   // columns 8-15 of row `tid`
+
+  if (a.fused_bwd) {   // dQ is accumulated into: clear this tile's rows (16 bytes per thread and step, coalesced)
+    for (int idx = tid; idx < kTile * 8; idx += 128) {
+      const int i = tile * kTile + (idx >> 3);
+      if (i < a.S) *reinterpret_cast<uint4*>(a.dq.row(b, h, i) + (idx & 7) * 8) = make_uint4(0u, 0u, 0u, 0u);
+    }
+  }
+  const float sink2 = a.fused_bwd ? a.sinks[h] * kLog2e : 0.f;
+  float sink_term = 0.f;   // this thread's rows' share of -sum 2^(sink - LSE) * delta
 
   uint4 xo[8], xd[8];
 #pragma unroll
@@ -78,17 +92,27 @@ __global__ void __launch_bounds__(128) attn_bwd_preprocess_kernel(const KernelAr
     if (part == 0) {
       const float lse = a.lse[row_base + r];
       a.delta[row_base + r] = s;  // zero for padding rows
-      a.delta[nlse_off + row_base + r] = -lse * kLog2e;
+      const float w = (a.fused_bwd && tile * kTile + r < len) ? fast_exp2(sink2 - lse * kLog2e) : 0.f;
+      a.delta[nlse_off + row_base + r] = a.fused_bwd ? w : -lse * kLog2e;
       uint32_t u0, u1, d0, d1;
       split_bf16x3(-lse * inv_scale, u0, u1);
       split_bf16x3(-s, d0, d1);
-      side_tile[side_offset(r, 0) >> 4] = make_uint4(u0, u1, d0, d1);   // r is the row within the tile
+      side_tile[side_offset(r) >> 4] = make_uint4(u0, u1, d0, d1);   // r is the row within the tile
+      sink_term -= w * (1.f - w) * s;
     }
   }
+  __shared__ float warp_term[4];
+  if (a.fused_bwd) {   // fixed-order tree: lanes, then the four warps
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) sink_term += __shfl_xor_sync(0xffffffffu, sink_term, off);
+    if (lane == 0) warp_term[warp] = sink_term;
+  }
   __syncthreads();
-  uint4* dst = reinterpret_cast<uint4*>(side_base + row_base * 32);   // this CTA's 128 rows
+  if (a.fused_bwd && tid == 0)
+    a.dsinks_partial[(((long long)h * a.B + b) * (a.S_pad / kTile) + tile) * a.partials_per_tile] =
+        (warp_term[0] + warp_term[1]) + (warp_term[2] + warp_term[3]);
+  uint4* dst = reinterpret_cast<uint4*>(side_base + row_base * kSideRowBytes);   // this CTA's 128 rows
   dst[tid] = side_tile[tid];
-  dst[tid + 128] = side_tile[tid + 128];
 }
 
 // grid (Hq), 256 threads

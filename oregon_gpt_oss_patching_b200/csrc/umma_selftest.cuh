@@ -19,8 +19,8 @@ namespace b200attn {
 struct SelftestSmem {
   alignas(1024) uint8_t a[kTileBytes];
   alignas(1024) uint8_t b[kTileBytes];
-  alignas(128) uint8_t a2[kSideTileBytes];
-  alignas(128) uint8_t b2[kSideTileBytes];
+  alignas(128) uint8_t a2[kOnesTileBytes];
+  alignas(128) uint8_t b2[kOnesTileBytes];
   alignas(8) uint64_t bar_load;
   uint64_t bar_mma;
   uint32_t tmem_base;
@@ -92,8 +92,8 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
     const uint4* rb = reinterpret_cast<const uint4*>(b_global + tid * 64);
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-      *reinterpret_cast<uint4*>(sm->a2 + side_offset(tid, half)) = ra[half];
-      *reinterpret_cast<uint4*>(sm->b2 + side_offset(tid, half)) = rb[half];
+      *reinterpret_cast<uint4*>(sm->a2 + ones_offset(tid, half)) = ra[half];
+      *reinterpret_cast<uint4*>(sm->b2 + ones_offset(tid, half)) = rb[half];
     }
     fence_proxy_async_smem();   // written with ordinary stores, read by the tensor core
   }
@@ -106,7 +106,7 @@ umma_selftest_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_cons
       const uint32_t idesc = make_idesc_bf16(128, 128, 0, 0);
       const uint64_t da = desc_kmajor(smem_u32(sm->a)), db = desc_kmajor(smem_u32(sm->b));
       for (int kk = 0; kk < 4; ++kk) umma_ss(tmem, da + kk * kDescKStepKMajor, db + kk * kDescKStepKMajor, idesc, kk > 0);
-      if (mode == 2) umma_ss(tmem, desc_side(smem_u32(sm->a2)), desc_side(smem_u32(sm->b2)), idesc, 1);
+      if (mode == 2) umma_ss(tmem, desc_ones(smem_u32(sm->a2)), desc_ones(smem_u32(sm->b2)), idesc, 1);
     } else {
       const uint32_t idesc = make_idesc_bf16(128, 64, 0, 1);
       const uint64_t db = desc_mnmajor(smem_u32(sm->b));

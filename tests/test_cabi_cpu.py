@@ -36,7 +36,7 @@ def test_helpers(lib):
     assert lib.b200attn_padded_len(129) == 256 and _cabi.padded_len(16384) == 16384
     p = _cabi.Params()
     p.B, p.Hq, p.S = 2, 64, 300
-    assert lib.b200attn_dsinks_scratch_floats(ctypes.byref(p)) == 64 * 2 * 3 * 8
+    assert lib.b200attn_dsinks_scratch_floats(ctypes.byref(p)) == 64 * 2 * 3 * 9
     for code in range(0, -9, -1):
         assert b"unknown" not in lib.b200attn_strerror(code)
     assert b"unknown" in lib.b200attn_strerror(-99)

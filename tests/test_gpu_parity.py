@@ -69,7 +69,11 @@ def test_lse_and_delta_stage(name):
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
     p.dq, p.dk, p.dv = (_cabi.tensor4(t, "bhsd") for t in (dq, dk, dv))
     assert lib.b200attn_fwd(ctypes.byref(p)) == 0
+    # the stages in the order b200attn_bwd runs them (for a narrow window the dkdv stage also makes dQ and the
+    # dq stage returns at once)
+    assert lib.b200attn_bwd_dq_is_fused(ctypes.byref(p)) == (1 if 0 < g["window"] <= 128 else 0)
     assert lib.b200attn_bwd_preprocess(ctypes.byref(p)) == 0
+    assert lib.b200attn_bwd_dkdv(ctypes.byref(p)) == 0
     assert lib.b200attn_bwd_dq(ctypes.byref(p)) == 0
     assert lib.b200attn_bwd_dsinks(ctypes.byref(p)) == 0
     torch.cuda.synchronize()
@@ -80,6 +84,10 @@ def test_lse_and_delta_stage(name):
         assert rel_err(lse[b, :, :L], g["triton_lse"][b, :, :L]) < TOL_LSE
         assert rel_err(delta[0, b, :, :L], want_delta[b, :, :L]) < 1e-5
         assert float(delta[0, b, :, L:].abs().max() if L < S_pad else 0.0) == 0.0
+        if lib.b200attn_bwd_dq_is_fused(ctypes.byref(p)):   # second plane: the sink's probability per row, 0 in padding
+            want_w = torch.exp(sinks[:, None] - lse[b, :, :L])
+            assert rel_err(delta[1, b, :, :L], want_w) < 1e-5
+            assert float(delta[1, b, :, L:].abs().max() if L < S_pad else 0.0) == 0.0
     assert rel_err(dsinks, g["hf_dsinks"]) < TOL_DSINKS
 
 
