@@ -32,8 +32,10 @@
 // exact as with c_i computed directly.
 //
 // Warps 0-7: compute (two warpgroups, 64 query columns each).  Warp 8: S^T/dP^T issuer (and tensor-
-// memory owner), 9: TMA loads, 10: dV/dK/dQ issuer, 11: TMA reductions of dQ, 12-15: dQ epilogue
-// (tensor memory -> bf16 -> shared memory).  Every wait is bounded.
+// memory owner), 9: TMA loads, 10: dV/dK issuer, 11: dQ issuer (an issuing thread gets few issue slots next to
+// the compute warps of its SM sub-partition: with two threads the 24 MMAs behind an item leave sooner; with
+// three -- dV, dK, dQ each on its own -- the kernel was slower again), 12-15: dQ epilogue
+// (tensor memory -> bf16 -> shared memory -> TMA reduction).  Every wait is bounded.
 #pragma once
 #include "attn_common.cuh"
 #include "bwd_dkdv_kernel.cuh"
@@ -63,11 +65,9 @@ struct FwSmem {
   uint64_t bar_s_full;        // S^T and dP^T ready                         (tcgen05.commit)
   uint64_t bar_s_free;        // S^T and dP^T are in registers              (256 arrivals)
   uint64_t bar_p_full;        // P^T (tensor memory) and dS^T (shared) written (256 arrivals)
-  uint64_t bar_p_free;        // the dV/dK/dQ MMAs have read them            (tcgen05.commit)
+  uint64_t bar_p_free;        // the dV/dK and the dQ MMAs have read them    (2 x tcgen05.commit)
   uint64_t bar_dq_full;       // an item's dQ is complete                    (tcgen05.commit)
   uint64_t bar_dq_free;       // ... and has been read out of tensor memory  (128 arrivals)
-  uint64_t bar_out_full;      // the staging tile is written                 (128 arrivals)
-  uint64_t bar_out_free;      // ... and has been read by the TMA engine     (1 arrival)
   uint64_t bar_acc;           // every MMA retired: dK/dV final
   uint32_t tmem_base;
   int abort_flag;
@@ -135,6 +135,22 @@ __device__ __forceinline__ void tma_reduce_add_4d(const void* tmap, uint32_t src
       : "memory");
 }
 
+// Barrier 1 among the 128 threads of the dQ epilogue warpgroup, returning the OR of their predicates.
+__device__ __forceinline__ bool epi_barrier_or(bool pred) {
+  uint32_t any;
+  asm volatile(
+      "{\n\t"
+      ".reg .pred p, q;\n\t"
+      "setp.ne.u32 q, %1, 0;\n\t"
+      "bar.red.or.pred p, 1, 128, q;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t"
+      "}\n"
+      : "=r"(any)
+      : "r"((uint32_t)pred)
+      : "memory");
+  return any != 0;
+}
+
 __global__ void __launch_bounds__(kFwThreads, 1)
 attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                              const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_do,
@@ -175,8 +191,7 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
   const uint32_t bar_kv = smem_u32(&sm->bar_kv), bar_acc = smem_u32(&sm->bar_acc), bar_s_full = smem_u32(&sm->bar_s_full),
                  bar_s_free = smem_u32(&sm->bar_s_free), bar_p_full = smem_u32(&sm->bar_p_full),
                  bar_p_free = smem_u32(&sm->bar_p_free), bar_dq_full = smem_u32(&sm->bar_dq_full),
-                 bar_dq_free = smem_u32(&sm->bar_dq_free), bar_out_full = smem_u32(&sm->bar_out_full),
-                 bar_out_free = smem_u32(&sm->bar_out_free);
+                 bar_dq_free = smem_u32(&sm->bar_dq_free);
   volatile int* abort_flag = &sm->abort_flag;
 
   if (tid == 0) {
@@ -188,11 +203,9 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
     mbar_init(bar_s_full, 1);
     mbar_init(bar_s_free, 2 * kComputeThreads);
     mbar_init(bar_p_full, 2 * kComputeThreads);
-    mbar_init(bar_p_free, 1);
+    mbar_init(bar_p_free, 2);
     mbar_init(bar_dq_full, 1);
     mbar_init(bar_dq_free, kComputeThreads);
-    mbar_init(bar_out_full, kComputeThreads);
-    mbar_init(bar_out_free, 1);
     mbar_init(bar_acc, 1);
     sm->abort_flag = 0;
     sm->loads_issued = 0;
@@ -233,12 +246,9 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
         tma_load_4d(smem_u32(sm->k), &tm_k, bar_kv, 0, kv0, g, b);
         tma_load_4d(smem_u32(sm->v), &tm_v, bar_kv, 0, kv0, g, b);
         int h = g * a.group, qi = 0;   // items run over a head's query tiles, then the next head of the group
-        for (int it = 0; it < n_items; ++it) {
+        auto issue_load = [&](int it) -> bool {
           const int s = it % kFwStages;
-          if (it >= kFwStages && !mbar_wait(smem_u32(&sm->bar_in_empty[s]), ((it / kFwStages) - 1) & 1, abort_flag)) {
-            report_abort(a);
-            break;
-          }
+          if (it >= kFwStages && !mbar_wait(smem_u32(&sm->bar_in_empty[s]), ((it / kFwStages) - 1) & 1, abort_flag)) return false;
           const int item_q0 = (qt_first + qi) * kTile;
           const uint32_t bar = smem_u32(&sm->bar_in_full[s]);
           const long long row_off = ((long long)(b * a.Hq + h)) * a.S_pad + item_q0;
@@ -252,7 +262,11 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
             qi = 0;
             ++h;
           }
-        }
+          return true;
+        };
+        bool ok = true;
+        for (int it = 0; ok && it < n_items; ++it) ok = issue_load(it);
+        if (!ok) report_abort(a);
       }
       __syncwarp();
     } else if (warp == 8) {
@@ -285,12 +299,11 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       }
       __syncwarp();
     } else if (warp == 10) {
-      // ------------------------- MMA issuer, dV, dK and dQ (back) -------------------------
+      // ------------------------------ MMA issuer, dV and dK ------------------------------
       if (lane == 0) {
         const uint32_t idesc_dv = make_idesc_bf16(kTile, kHeadDim, 0, 1);   // A in TMEM, B read N-contiguous
         const uint32_t idesc_dk = make_idesc_bf16(kTile, kHeadDim, 0, 1);   // A = dS^T K-contiguous, B = Q read N-contiguous
-        const uint32_t idesc_dq = make_idesc_bf16(kTile, kHeadDim, 1, 1);   // A = dS^T read M-contiguous, B = K read N-contiguous
-        const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k));
+        const uint32_t ds_base = smem_u32(sm->ds[0]);
         bool ok = true;
         for (int it = 0; ok && it < n_items; ++it) {
           if (!(ok = mbar_wait(bar_p_full, it & 1, abort_flag))) break;
@@ -298,9 +311,6 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
           const int s = it % kFwStages;
           const uint64_t dot_desc = desc_mnmajor(smem_u32(sm->d_o[s]));
           const uint64_t qt_desc = desc_mnmajor(smem_u32(sm->q[s]));
-          const uint32_t ds_base = smem_u32(sm->ds[0]);
-          // dS^T with queries as the M dimension: two 64-query panels kTileBytes apart, 8-key groups 1024 B apart
-          const uint64_t ds_mn_desc = make_smem_desc_sw128(ds_base, kTileBytes, 1024);
 #pragma unroll
           for (int kk = 0; kk < kTile / 16; ++kk)
             umma_ts(tmem_dv, tmem_pt + kk * 8, dot_desc + kk * kDescKStepMNMajor, idesc_dv, (it > 0 || kk > 0) ? 1u : 0u);
@@ -308,6 +318,23 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
           for (int kk = 0; kk < kTile / 16; ++kk)   // k-step kk = queries 16kk..16kk+15: panel kk/4, 32 bytes per step inside it
             umma_ss(tmem_dk, desc_kmajor(ds_base + (kk >> 2) * kTileBytes) + (kk & 3) * kDescKStepKMajor,
                     qt_desc + kk * kDescKStepMNMajor, idesc_dk, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(bar_p_free);
+          umma_commit(smem_u32(&sm->bar_in_empty[s]));
+          if (it == n_items - 1) umma_commit(bar_acc);
+        }
+        if (!ok) report_abort(a);
+      }
+      __syncwarp();
+    } else {
+      // --------------------------------- MMA issuer, dQ ---------------------------------
+      if (lane == 0) {
+        const uint32_t idesc_dq = make_idesc_bf16(kTile, kHeadDim, 1, 1);   // A = dS^T read M-contiguous, B = K read N-contiguous
+        // dS^T with queries as the M dimension: two 64-query panels kTileBytes apart, 8-key groups 1024 B apart
+        const uint64_t ds_mn_desc = make_smem_desc_sw128(smem_u32(sm->ds[0]), kTileBytes, 1024);
+        const uint64_t kt_desc = desc_mnmajor(smem_u32(sm->k));
+        bool ok = mbar_wait(bar_kv, 0, abort_flag);
+        for (int it = 0; ok && it < n_items; ++it) {
+          if (!(ok = mbar_wait(bar_p_full, it & 1, abort_flag))) break;
           // the previous item's dQ must have left tensor memory
           if (it > 0 && !(ok = mbar_wait(bar_dq_free, (it - 1) & 1, abort_flag))) break;
           tc_fence_after_sync();
@@ -315,31 +342,8 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
           for (int kk = 0; kk < kTile / 16; ++kk)   // k-step kk = keys 16kk..16kk+15
             umma_ss(tmem_dq, ds_mn_desc + kk * kDescKStepMNMajor, kt_desc + kk * kDescKStepMNMajor, idesc_dq, kk > 0 ? 1u : 0u);
           umma_commit(bar_p_free);
-          umma_commit(smem_u32(&sm->bar_in_empty[s]));
           umma_commit(bar_dq_full);
-          if (it == n_items - 1) umma_commit(bar_acc);
         }
-        if (!ok) report_abort(a);
-      }
-      __syncwarp();
-    } else {
-      // ------------------------------ TMA reductions of dQ ------------------------------
-      if (lane == 0) {
-        prefetch_tmap(&tm_dq);
-        bool ok = true;
-        int h = g * a.group, qi = 0;
-        for (int it = 0; ok && it < n_items; ++it) {
-          if (!(ok = mbar_wait(bar_out_full, it & 1, abort_flag))) break;
-          tma_reduce_add_4d(&tm_dq, smem_u32(sm->dq_out), 0, (qt_first + qi) * kTile, h, b);   // rows past the end are clipped
-          tma_store_commit();
-          tma_store_wait_read();       // the tile has been read: the next item's rows may land
-          mbar_arrive(bar_out_free);
-          if (++qi == nq) {
-            qi = 0;
-            ++h;
-          }
-        }
-        tma_store_wait_all();
         if (!ok) report_abort(a);
       }
       __syncwarp();
@@ -351,11 +355,18 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       const int r = tid & 127;               // query row of the item's tile = tensor-memory lane
       const uint32_t lane_addr = uint32_t((warp & 3) * 32) << 16;
       bool ok = true;
-      for (int it = 0; ok && it < n_items; ++it) {
-        if (!(ok = warp_all(mbar_wait(bar_dq_full, it & 1, abort_flag)))) break;
+      int h = g * a.group, qi = 0;
+      if (r == 0) prefetch_tmap(&tm_dq);
+      for (int it = 0; it < n_items; ++it) {
+        ok = mbar_wait(bar_dq_full, it & 1, abort_flag);
         tc_fence_after_sync();
-        // the previous item's reduction must have read the staging tile
-        if (it >= 1 && !(ok = warp_all(mbar_wait(bar_out_free, (it - 1) & 1, abort_flag)))) break;
+        // the previous item's reduction (issued by thread 0 of this warpgroup) must have read the staging tile
+        if (r == 0) tma_store_wait_read();
+        // one answer for the whole warpgroup (a thread that left alone would strand the others at the next barrier)
+        if (epi_barrier_or(!ok || *abort_flag != 0)) {
+          ok = false;
+          break;
+        }
         uint8_t* const out_row = sm->dq_out + r * 128;
         const float sc = a.scale;
 #pragma unroll 1
@@ -376,8 +387,17 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
                            pack_bf16(__uint_as_float(r0[c * 8 + 6]) * sc, __uint_as_float(r0[c * 8 + 7]) * sc));
         }
         fence_proxy_async_smem();
-        mbar_arrive(bar_out_full);
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (r == 0) {
+          tma_reduce_add_4d(&tm_dq, smem_u32(sm->dq_out), 0, (qt_first + qi) * kTile, h, b);   // rows past the end are clipped
+          tma_store_commit();
+        }
+        if (++qi == nq) {
+          qi = 0;
+          ++h;
+        }
       }
+      if (r == 0) tma_store_wait_all();
       if (!ok && r == 0) report_abort(a);
     }
   } else {
