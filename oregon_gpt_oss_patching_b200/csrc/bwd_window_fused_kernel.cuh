@@ -102,32 +102,7 @@ __device__ __forceinline__ void fw_compute_chunk(const uint32_t (&rs)[32], const
   }
 }
 
-template <bool kMask>
-__device__ __forceinline__ void fw_compute(const uint32_t (&rs)[2][32], const uint32_t (&rp)[2][32], float scale_log2,
-                                           int i0, int j, int window, int len, const float* w, float2& acc,
-                                           uint32_t (&pp)[2][16], uint32_t (&pd)[2][16]) {
-  const float2 scale2 = make_float2(scale_log2, scale_log2);
-#pragma unroll
-  for (int c = 0; c < 2; ++c) {
-    if (kMask) {   // every 32-query chunk is classified for the whole warp: nobody sees it, everybody does, or mixed
-      const uint32_t bits = visible_queries32(j, i0 + c * 32, window, len);
-      if (__all_sync(0xffffffffu, bits == 0u)) {
-#pragma unroll
-        for (int k = 0; k < 16; ++k) {
-          pp[c][k] = 0u;
-          pd[c][k] = 0u;
-        }
-      } else if (__all_sync(0xffffffffu, bits == 0xffffffffu)) {
-        fw_compute_chunk<false>(rs[c], rp[c], scale2, bits, w + c * 32, acc, pp[c], pd[c]);
-      } else {
-        fw_compute_chunk<true>(rs[c], rp[c], scale2, bits, w + c * 32, acc, pp[c], pd[c]);
-      }
-    } else {
-      fw_compute_chunk<false>(rs[c], rp[c], scale2, 0xffffffffu, w + c * 32, acc, pp[c], pd[c]);
-    }
-  }
-}
-
+// One (128 x 64) bf16 tile from shared memory ADDED to the tensor in global memory by the TMA engine.
 __device__ __forceinline__ void tma_reduce_add_4d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2, int c3) {
   asm volatile(
       "cp.reduce.async.bulk.tensor.4d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
@@ -416,20 +391,47 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
       for (int it = 0; it < n_items; ++it, qi = (qi + 1 == nq) ? 0 : qi + 1) {
         const int i0 = (qt_first + qi) * kTile + wg * 64;  // first query column of this thread
         const float* w = sm->w[it % kFwStages] + wg * 64;
-        const bool need_mask = (kv0 + kTile - 1 > i0) || (kv0 <= i0 + 63 - a.window) || (i0 + 64 > len);
         if (!(ok = warp_all(mbar_wait(bar_s_full, it & 1, abort_flag)))) break;
         tc_fence_after_sync();
-        uint32_t rs[2][32], rp[2][32];
-        tmem_ld32(tmem_st + lane_addr + wg * 64, rs[0]);
-        tmem_ld32(tmem_dpt + lane_addr + wg * 64, rp[0]);
-        tmem_ld32(tmem_st + lane_addr + wg * 64 + 32, rs[1]);
-        tmem_ld32(tmem_dpt + lane_addr + wg * 64 + 32, rp[1]);
-        tmem_wait_ld();
-        tc_fence_before_sync();
-        mbar_arrive(bar_s_free);
+        // The thread's 64 columns in two chunks of 32 by a ROLLED loop (one copy of the arithmetic in the
+        // instruction cache, 64 instead of 128 score registers alive).  Every chunk is classified for the whole
+        // warp: visible to nobody (zeros, no exponential -- half the chunks of these layers), to everybody (no
+        // masking work), or mixed.
         uint32_t pp[2][16], pd[2][16];
-        if (need_mask) fw_compute<true>(rs, rp, a.scale_log2, i0, j, a.window, len, w, sink_acc, pp, pd);
-        else fw_compute<false>(rs, rp, a.scale_log2, i0, j, a.window, len, w, sink_acc, pp, pd);
+        const float2 scale2 = make_float2(a.scale_log2, a.scale_log2);
+#pragma unroll 1
+        for (int c = 0; c < 2; ++c) {
+          uint32_t rs[32], rp[32], tp[16], td[16];
+          tmem_ld32(tmem_st + lane_addr + wg * 64 + c * 32, rs);
+          tmem_ld32(tmem_dpt + lane_addr + wg * 64 + c * 32, rp);
+          tmem_wait_ld();
+          if (c == 1) {   // S^T/dP^T are out of tensor memory: the next item's may be computed
+            tc_fence_before_sync();
+            mbar_arrive(bar_s_free);
+          }
+          const uint32_t bits = visible_queries32(j, i0 + c * 32, a.window, len);
+          if (__all_sync(0xffffffffu, bits == 0u)) {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) {
+              tp[k] = 0u;
+              td[k] = 0u;
+            }
+          } else if (__all_sync(0xffffffffu, bits == 0xffffffffu)) {
+            fw_compute_chunk<false>(rs, rp, scale2, bits, w + c * 32, sink_acc, tp, td);
+          } else {
+            fw_compute_chunk<true>(rs, rp, scale2, bits, w + c * 32, sink_acc, tp, td);
+          }
+#pragma unroll
+          for (int k = 0; k < 16; ++k) {   // (the loop is rolled, so the chunk index cannot select the registers)
+            if (c == 0) {
+              pp[0][k] = tp[k];
+              pd[0][k] = td[k];
+            } else {
+              pp[1][k] = tp[k];
+              pd[1][k] = td[k];
+            }
+          }
+        }
         if (qi + 1 == nq) {   // the head's last item: this warp's partial, lanes added in a fixed order
           float t = sink_acc.x + sink_acc.y;
 #pragma unroll
