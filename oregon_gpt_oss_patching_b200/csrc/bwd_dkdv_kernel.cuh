@@ -155,13 +155,13 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
     mbar_init(bar_kv, 1);
     for (int s = 0; s < kDkvStages; ++s) {
       mbar_init(smem_u32(&sm->bar_in_full[s]), 1);
-      mbar_init(smem_u32(&sm->bar_in_empty[s]), 1);
+      mbar_init(smem_u32(&sm->bar_in_empty[s]), 2);
     }
     mbar_init(bar_s_full, 1);
     mbar_init(bar_s_free, 2 * kComputeThreads);
     mbar_init(bar_p_full, 2 * kComputeThreads);
-    mbar_init(bar_p_free, 1);
-    mbar_init(bar_acc, 1);
+    mbar_init(bar_p_free, 2);
+    mbar_init(bar_acc, 2);
     sm->abort_flag = 0;
     sm->loads_issued = 0;
     fence_mbar_init();
@@ -258,23 +258,23 @@ attn_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_cons
       if (!ok) report_abort(a);
     }
     __syncwarp();
-  } else if (warp == 10) {
-    // ---------------------------- MMA issuer, dV and dK (back) ----------------------------
+  } else {
+    // ------------- MMA issuers, dV (warp 10) and dK (warp 11), on two SM sub-partitions -------------
+    // An issuing thread gets few issue slots next to the compute warps of its sub-partition; the two
+    // products are independent, so each has a thread of its own.  Every barrier they release counts two commits.
     if (lane == 0) {
       const uint32_t idesc_back = make_idesc_bf16(kTile, kHeadDim, 0, 1);  // A in TMEM, B read N-contiguous
+      const bool is_dv = warp == 10;
+      const uint32_t acc = is_dv ? tmem_dv : tmem_dk, src = is_dv ? tmem_pt : tmem_dst;
       bool ok = true;
       for (int it = 0; ok && it < n_items; ++it) {
         if (!(ok = mbar_wait(bar_p_full, it & 1, abort_flag))) break;   // P^T/dS^T of the item have been written
         tc_fence_after_sync();
         const int s = it % kDkvStages;
-        const uint64_t dot_desc = desc_mnmajor(smem_u32(sm->d_o[s]));
-        const uint64_t qt_desc = desc_mnmajor(smem_u32(sm->q[s]));
+        const uint64_t b_desc = desc_mnmajor(smem_u32(is_dv ? sm->d_o[s] : sm->q[s]));
 #pragma unroll
         for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem_dv, tmem_pt + kk * 8, dot_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
-#pragma unroll
-        for (int kk = 0; kk < kTile / 16; ++kk)
-          umma_ts(tmem_dk, tmem_dst + kk * 8, qt_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
+          umma_ts(acc, src + kk * 8, b_desc + kk * kDescKStepMNMajor, idesc_back, (it > 0 || kk > 0) ? 1u : 0u);
         umma_commit(bar_p_free);                      // P^T/dS^T columns reusable once these retire
         umma_commit(smem_u32(&sm->bar_in_empty[s]));  // and so is the Q/dO stage (its S^T/dP^T MMAs retired before P^T was written)
         if (it == n_items - 1) umma_commit(bar_acc);
