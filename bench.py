@@ -683,6 +683,7 @@ def main():
                     "(default: $REFERENCE_PATH, then baseline/_ref)")
     ap.add_argument("--no-contender", action="store_true", help="skip the reference-Triton-kernel arm")
     ap.add_argument("--no-strong", action="store_true", help="skip the sharded (strong-scaling) records at N > 1")
+    ap.add_argument("--moe-tokens", type=int, default=8192, help="tokens of `--workload moe` (one expert block, fwd+bwd)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -692,6 +693,10 @@ def main():
         return
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the attention path has no CPU implementation")
+    if args.workload == "moe":   # the block after attention in every layer: a separate line, not the headline metric
+        from bench_moe import run_moe
+        run_moe(args, rank, world, local_rank)
+        return
     run_b200(args, rank, world, local_rank)
 
 

@@ -1,4 +1,4 @@
-"""ctypes binding of ``libb200attn.so`` (the C ABI declared in ``include/b200attn.h``).
+"""ctypes binding of ``libb200attn.so`` (the C ABI declared in ``include/b200attn.h`` and ``include/b200moe.h``).
 
 There is deliberately no fallback: if the library cannot be loaded, or a call returns an
 error code, a ``RuntimeError`` is raised.
@@ -18,6 +18,8 @@ EXPORTS = (
     "b200attn_fwd", "b200attn_bwd", "b200attn_bwd_preprocess", "b200attn_bwd_dsinks", "b200attn_bwd_dkdv",
     "b200attn_bwd_dq", "b200attn_bwd_dq_is_fused", "b200attn_bwd_static_scratch", "b200attn_umma_selftest",
     "b200attn_wait_selftest",
+    "b200moe_sizeof_gemm_params", "b200moe_grouped_gemm", "b200moe_gather_rows", "b200moe_combine_rows", "b200moe_row_dot",
+    "b200moe_glu", "b200moe_glu_bwd", "b200moe_bias_grad",
 )
 
 ROW_TILE = 128
@@ -41,6 +43,20 @@ class Params(ctypes.Structure):
         ("q", Tensor4), ("k", Tensor4), ("v", Tensor4), ("o", Tensor4), ("lse", ctypes.c_void_p),
         ("d_o", Tensor4), ("dq", Tensor4), ("dk", Tensor4), ("dv", Tensor4),
         ("delta", ctypes.c_void_p), ("dsinks", ctypes.c_void_p), ("dsinks_partial", ctypes.c_void_p),
+    ]
+
+
+MOE_ROW_ALIGN = 128          # B200MOE_ROW_ALIGN
+MOE_ROWS_NN, MOE_ROWS_NT, MOE_INNER_TN = 0, 1, 2
+
+
+class MoeGemmParams(ctypes.Structure):
+    """``b200moe_gemm_params`` -- field order and types mirror include/b200moe.h exactly."""
+    _fields_ = [
+        ("op", ctypes.c_int32), ("num_groups", ctypes.c_int32), ("rows", ctypes.c_int32),
+        ("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
+        ("offsets", ctypes.c_void_p), ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("bias", ctypes.c_void_p),
+        ("d", ctypes.c_void_p), ("device", ctypes.c_int32), ("stream", ctypes.c_void_p), ("status", ctypes.c_void_p),
     ]
 
 
@@ -89,6 +105,24 @@ def load() -> ctypes.CDLL:
                                                ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         lib.b200attn_wait_selftest.restype = ctypes.c_int
         lib.b200attn_wait_selftest.argtypes = [ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+        lib.b200moe_sizeof_gemm_params.restype = ctypes.c_size_t
+        lib.b200moe_sizeof_gemm_params.argtypes = []
+        if lib.b200moe_sizeof_gemm_params() != ctypes.sizeof(MoeGemmParams):
+            raise RuntimeError("b200moe_gemm_params layout mismatch between libb200attn.so and its Python mirror")
+        lib.b200moe_grouped_gemm.restype = ctypes.c_int
+        lib.b200moe_grouped_gemm.argtypes = [ctypes.POINTER(MoeGemmParams)]
+        for name, args in (
+            ("b200moe_gather_rows", [vp, vp, vp, vp, i32, i32, i32, vp]),
+            ("b200moe_combine_rows", [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+            ("b200moe_row_dot", [vp, vp, vp, vp, i32, i32, i32, i32, vp]),
+            ("b200moe_glu", [vp, vp, i64, i32, i32, vp]),
+            ("b200moe_glu_bwd", [vp, vp, vp, i64, i32, i32, vp]),
+            ("b200moe_bias_grad", [vp, vp, vp, i32, i32, i32, vp]),
+        ):
+            fn = getattr(lib, name)
+            fn.restype = ctypes.c_int
+            fn.argtypes = args
         _lib = lib
     return _lib
 

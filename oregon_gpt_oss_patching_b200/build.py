@@ -10,7 +10,8 @@ _PKG = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_PKG, "csrc")
 LIB_DIR = os.path.join(_PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libb200attn.so")
-HEADER = os.path.join(os.path.dirname(_PKG), "include", "b200attn.h")
+HEADERS = [os.path.join(os.path.dirname(_PKG), "include", h) for h in ("b200attn.h", "b200moe.h")]
+UNITS = ("b200attn_api.cu", "b200moe_api.cu")   # one translation unit per header
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -19,7 +20,7 @@ NVCC_FLAGS = [
 
 
 def _sources():
-    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cuh")) + [HEADER])
+    return sorted(glob.glob(os.path.join(CSRC, "*.cu")) + glob.glob(os.path.join(CSRC, "*.cuh")) + HEADERS)
 
 
 def is_stale() -> bool:
@@ -37,14 +38,14 @@ def find_nvcc() -> str | None:
 
 
 def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile ``csrc/b200attn_api.cu`` (which includes every kernel) into ``lib/libb200attn.so``."""
+    """Compile the translation units of ``csrc/`` (each includes its kernels) into ``lib/libb200attn.so``."""
     if not force and not is_stale():
         return LIB_PATH
     nvcc = find_nvcc()
     if nvcc is None:
         raise RuntimeError("nvcc not found: cannot build libb200attn.so")
     os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, os.path.join(CSRC, "b200attn_api.cu")]
+    cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, *[os.path.join(CSRC, u) for u in UNITS]]
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     subprocess.check_call(cmd)

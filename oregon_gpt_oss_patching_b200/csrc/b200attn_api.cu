@@ -9,6 +9,7 @@
 #include <mutex>
 
 #include "attn_common.cuh"
+#include "host_common.cuh"
 #include "bwd_dkdv_kernel.cuh"
 #include "bwd_dq_kernel.cuh"
 #include "bwd_dq_persistent_kernel.cuh"
@@ -21,45 +22,7 @@
 namespace {
 
 using namespace b200attn;
-
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// The driver entry point is looked up once; the pointer is immutable afterwards.
-EncodeTiledFn encode_tiled_fn() {
-  static EncodeTiledFn fn = []() -> EncodeTiledFn {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
-        q != cudaDriverEntryPointSuccess)
-      return nullptr;
-    return reinterpret_cast<EncodeTiledFn>(p);
-  }();
-  return fn;
-}
-
-// Makes `device` current for the duration of a call and restores the caller's device after.
-struct DeviceGuard {
-  int prev = -1;
-  bool ok = true;
-  explicit DeviceGuard(int device) {
-    if (cudaGetDevice(&prev) != cudaSuccess) { ok = false; return; }
-    if (prev != device && cudaSetDevice(device) != cudaSuccess) ok = false;
-  }
-  ~DeviceGuard() {
-    int cur = -1;
-    if (prev >= 0 && cudaGetDevice(&cur) == cudaSuccess && cur != prev) cudaSetDevice(prev);
-  }
-};
-
-int check_device(int device) {
-  int major = 0;
-  if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, device) != cudaSuccess) return B200ATTN_ECUDA;
-  return major == 10 ? B200ATTN_OK : B200ATTN_EDEVICE;
-}
-
-bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+using namespace b200attn::host;
 
 // A dimension of extent 1 may carry any stride; give it a harmless one.
 int64_t usable_stride(int64_t stride, int64_t extent, int64_t fallback) { return extent == 1 ? fallback : stride; }
@@ -149,22 +112,6 @@ KernelArgs make_args(const b200attn_params* p) {
   return a;
 }
 
-// Raises a kernel's dynamic shared-memory limit.  The attribute belongs to the (kernel, device) pair and
-// never changes afterwards, so it is set once per pair instead of on every launch.
-constexpr int kMaxDevices = 64;
-template <auto kKernel>
-int set_smem(size_t bytes) {
-  static std::atomic<bool> done[kMaxDevices];   // one array per kernel; zero-initialised
-  int device = -1;
-  if (cudaGetDevice(&device) != cudaSuccess) return B200ATTN_ECUDA;
-  const bool cacheable = device >= 0 && device < kMaxDevices;
-  if (cacheable && done[device].load(std::memory_order_acquire)) return B200ATTN_OK;
-  if (cudaFuncSetAttribute(kKernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes) != cudaSuccess)
-    return B200ATTN_ECUDA;
-  if (cacheable) done[device].store(true, std::memory_order_release);
-  return B200ATTN_OK;
-}
-
 // Layers the head-packed kernels serve: a causal window of at most 128 keys with 8 query heads per KV head.
 bool packed_window_layer(const b200attn_params* p) {
   return p->window > 0 && p->window <= kPkMaxWindow && p->Hq / p->Hkv == kPkHeads;
@@ -174,7 +121,7 @@ bool packed_window_layer(const b200attn_params* p) {
 // contributions can be added in global memory without the result depending on their order.
 bool fused_window_bwd(const b200attn_params* p) { return p->window > 0 && p->window <= kFwMaxWindow; }
 
-int launch_status() { return cudaGetLastError() == cudaSuccess ? B200ATTN_OK : B200ATTN_ECUDA; }
+
 
 }  // namespace
 

@@ -1,0 +1,188 @@
+// C ABI of the mixture-of-experts entry points (declared in include/b200moe.h): argument validation,
+// TMA tensor maps, kernel launches.  No device memory is allocated here and nothing synchronises.
+#include "../../include/b200moe.h"
+
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include "host_common.cuh"
+#include "moe_aux_kernels.cuh"
+#include "moe_gemm_kernel.cuh"
+
+namespace {
+
+using namespace b200moe;
+using namespace b200attn::host;
+
+// 3-D bf16 map (inner, rows, groups) with the 128-byte swizzle; the inner box extent is always 64 elements.
+int make_map3(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+  EncodeTiledFn fn = encode_tiled_fn();
+  if (fn == nullptr) return B200ATTN_ECUDA;
+  cuuint64_t dims[3] = {inner, rows, groups};
+  cuuint64_t strides[2] = {inner * 2, inner * rows * 2};
+  cuuint32_t box[3] = {64, box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ETENSORMAP;
+}
+
+int sm_count(int device) {
+  int n = 0;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) return 148;
+  return n;
+}
+
+int elementwise_grid(long long work_items, int block, int device) {
+  const long long want = (work_items + block - 1) / block;
+  const long long cap = (long long)sm_count(device) * 16;
+  return (int)(want < 1 ? 1 : (want > cap ? cap : want));
+}
+
+int check_matrix(const void* p, int64_t cols) {
+  if (p == nullptr) return B200ATTN_EINVAL;
+  if (!aligned16(p) || cols % 8 != 0) return B200ATTN_EALIGN;
+  return B200ATTN_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t b200moe_sizeof_gemm_params(void) { return sizeof(b200moe_gemm_params); }
+
+int b200moe_grouped_gemm(const b200moe_gemm_params* p) {
+  if (p == nullptr || p->offsets == nullptr || p->a == nullptr || p->b == nullptr || p->d == nullptr) return B200ATTN_EINVAL;
+  if (p->op < B200MOE_ROWS_NN || p->op > B200MOE_INNER_TN) return B200ATTN_EINVAL;
+  if (p->num_groups <= 0 || p->num_groups > B200MOE_MAX_GROUPS || p->rows <= 0 || p->rows % B200MOE_ROW_ALIGN != 0) return B200ATTN_ESHAPE;
+  const bool inner = p->op == B200MOE_INNER_TN;
+  if (p->N <= 0 || (inner ? p->M <= 0 : p->K <= 0)) return B200ATTN_EINVAL;
+  if (p->N % 8 != 0 || (inner ? p->M % 8 != 0 : p->K % 8 != 0)) return B200ATTN_EALIGN;
+  if (!aligned16(p->a) || !aligned16(p->b) || !aligned16(p->d) || (p->bias != nullptr && !aligned16(p->bias))) return B200ATTN_EALIGN;
+  if (inner && p->bias != nullptr) return B200ATTN_EINVAL;
+  int rc = check_device(p->device);
+  if (rc) return rc;
+  DeviceGuard guard(p->device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+
+  GemmArgs a{};
+  a.mode = inner ? 1 : 0;
+  a.num_groups = p->num_groups;
+  a.M = inner ? p->M : 0;
+  a.N = p->N;
+  a.K = inner ? 0 : p->K;
+  a.offsets = p->offsets;
+  a.bias = static_cast<const __nv_bfloat16*>(p->bias);
+  a.status = p->status;
+  CUtensorMap ta, tb, td;
+  long long max_tiles;
+  const long long n_tiles = (p->N + kBN - 1) / kBN;
+  if (!inner) {
+    a.a_mn = 0;
+    a.b_mn = p->op == B200MOE_ROWS_NN ? 1 : 0;
+    if ((rc = make_map3(&ta, p->a, p->K, p->rows, 1, kHalfM))) return rc;                        // (64 inner x 128 rows) boxes
+    if (a.b_mn) {
+      if ((rc = make_map3(&tb, p->b, p->N, p->K, p->num_groups, 64))) return rc;                 // (64 columns x 64 inner rows) panels
+    } else {
+      if ((rc = make_map3(&tb, p->b, p->K, p->N, p->num_groups, kBN))) return rc;                // (64 inner x 192 rows) boxes
+    }
+    if ((rc = make_map3(&td, p->d, p->N, p->rows, 1, kHalfM))) return rc;
+    max_tiles = ((long long)p->rows / kHalfM + p->num_groups) * n_tiles;   // an upper bound; the kernel counts the real ones
+  } else {
+    a.a_mn = 1;
+    a.b_mn = 1;
+    if ((rc = make_map3(&ta, p->a, p->M, p->rows, 1, 64))) return rc;
+    if ((rc = make_map3(&tb, p->b, p->N, p->rows, 1, 64))) return rc;
+    if ((rc = make_map3(&td, p->d, p->N, p->M, p->num_groups, kHalfM))) return rc;
+    max_tiles = (long long)p->num_groups * ((p->M + kBM - 1) / kBM) * n_tiles;
+  }
+  const size_t smem = sizeof(GemmSmem) + 1024;
+  if ((rc = set_smem<moe_grouped_gemm_kernel>(smem))) return rc;
+  const long long sms = sm_count(p->device);
+  const int grid = (int)(max_tiles < sms ? max_tiles : sms);
+  moe_grouped_gemm_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(ta, tb, td, a);
+  return launch_status();
+}
+
+int b200moe_gather_rows(const void* src, const int32_t* row_src, const float* row_scale, void* out, int32_t rows,
+                        int32_t cols, int32_t device, void* stream) {
+  if (row_src == nullptr || rows <= 0 || cols <= 0) return B200ATTN_EINVAL;
+  int rc;
+  if ((rc = check_matrix(src, cols)) || (rc = check_matrix(out, cols)) || (rc = check_device(device))) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const int grid = elementwise_grid((long long)rows * (cols / 8), 256, device);
+  moe_gather_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), row_src, row_scale, static_cast<__nv_bfloat16*>(out), rows, cols);
+  return launch_status();
+}
+
+int b200moe_combine_rows(const void* y, const int32_t* pos, const float* weights, void* out, int32_t tokens,
+                         int32_t top_k, int32_t cols, int32_t device, void* stream) {
+  if (pos == nullptr || tokens <= 0 || top_k <= 0 || cols <= 0) return B200ATTN_EINVAL;
+  int rc;
+  if ((rc = check_matrix(y, cols)) || (rc = check_matrix(out, cols)) || (rc = check_device(device))) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const int grid = elementwise_grid((long long)tokens * (cols / 8), 256, device);
+  moe_combine_rows_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y), pos, weights, static_cast<__nv_bfloat16*>(out), tokens, top_k, cols);
+  return launch_status();
+}
+
+int b200moe_row_dot(const void* g, const void* y, const int32_t* pos, float* dots, int32_t tokens, int32_t top_k,
+                    int32_t cols, int32_t device, void* stream) {
+  if (pos == nullptr || dots == nullptr || tokens <= 0 || top_k <= 0 || cols <= 0) return B200ATTN_EINVAL;
+  int rc;
+  if ((rc = check_matrix(g, cols)) || (rc = check_matrix(y, cols)) || (rc = check_device(device))) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const int pairs = tokens * top_k;
+  const int grid = elementwise_grid((long long)pairs * 32, 256, device);
+  moe_row_dot_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(g), static_cast<const __nv_bfloat16*>(y), pos, dots, pairs, top_k, cols);
+  return launch_status();
+}
+
+int b200moe_glu(const void* y1, void* h, int64_t rows, int32_t cols_h, int32_t device, void* stream) {
+  if (rows <= 0 || cols_h <= 0) return B200ATTN_EINVAL;
+  int rc;
+  if ((rc = check_matrix(y1, 2 * (int64_t)cols_h)) || (rc = check_matrix(h, cols_h)) || (rc = check_device(device))) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const int grid = elementwise_grid(rows * (cols_h / 8), 256, device);
+  moe_glu_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(y1),
+                                                                       static_cast<__nv_bfloat16*>(h), rows, cols_h);
+  return launch_status();
+}
+
+int b200moe_glu_bwd(const void* y1, const void* dh, void* dy1, int64_t rows, int32_t cols_h, int32_t device,
+                    void* stream) {
+  if (rows <= 0 || cols_h <= 0) return B200ATTN_EINVAL;
+  int rc;
+  if ((rc = check_matrix(y1, 2 * (int64_t)cols_h)) || (rc = check_matrix(dy1, 2 * (int64_t)cols_h)) ||
+      (rc = check_matrix(dh, cols_h)) || (rc = check_device(device)))
+    return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const int grid = elementwise_grid(rows * (cols_h / 8), 256, device);
+  moe_glu_bwd_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(y1), static_cast<const __nv_bfloat16*>(dh), static_cast<__nv_bfloat16*>(dy1), rows, cols_h);
+  return launch_status();
+}
+
+int b200moe_bias_grad(const void* dy, const int32_t* offsets, void* db, int32_t num_groups, int32_t cols,
+                      int32_t device, void* stream) {
+  if (offsets == nullptr || num_groups <= 0 || cols <= 0) return B200ATTN_EINVAL;
+  int rc;
+  if ((rc = check_matrix(dy, cols)) || (rc = check_matrix(db, cols)) || (rc = check_device(device))) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  const dim3 grid((cols / 2 + 255) / 256, num_groups);
+  moe_bias_grad_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(dy), offsets,
+                                                                             static_cast<__nv_bfloat16*>(db), cols);
+  return launch_status();
+}
+
+}  // extern "C"

@@ -1,0 +1,168 @@
+// The memory-bound steps around the grouped GEMMs of the mixture-of-experts block: moving token rows into
+// and out of the expert-sorted buffer, the gated activation and its derivative, and the bias gradients.
+// They stand in for the indexing and elementwise tensor operations of GptOssExperts.forward
+// (transformers/models/gpt_oss/modeling_gpt_oss.py:76-82 `_apply_gate`, :104 `hidden_states[token_idx]`,
+// :108-109 `out * routing_weights[...]`, `index_add_`) and for what autograd derives from them.  Every sum is
+// taken in a fixed order in fp32 (the index_add_ of the original accumulates bf16 values with atomics).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace b200moe {
+
+constexpr float kGluAlpha = 1.702f;   // GptOssExperts.alpha
+constexpr float kGluLimit = 7.0f;     // GptOssExperts.limit
+
+__device__ __forceinline__ float bf16_lo(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16_hi(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// out[r, :] = src[row_src[r], :] * (row_scale ? row_scale[r] : 1)   when row_src[r] >= 0, zeros otherwise.
+// One thread moves 16 bytes; `cols` is a multiple of 8.
+__global__ void moe_gather_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ row_src,
+                                       const float* __restrict__ row_scale, __nv_bfloat16* __restrict__ out,
+                                       int rows, int cols) {
+  const int vec_per_row = cols >> 3;
+  const long long total = (long long)rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int r = (int)(i / vec_per_row), c = (int)(i - (long long)r * vec_per_row);
+    const int s = row_src[r];
+    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+    if (s >= 0) {
+      v = __ldg(reinterpret_cast<const uint4*>(src + (long long)s * cols) + c);
+      if (row_scale != nullptr) {
+        const float w = row_scale[r];
+        v.x = pack2(bf16_lo(v.x) * w, bf16_hi(v.x) * w);
+        v.y = pack2(bf16_lo(v.y) * w, bf16_hi(v.y) * w);
+        v.z = pack2(bf16_lo(v.z) * w, bf16_hi(v.z) * w);
+        v.w = pack2(bf16_lo(v.w) * w, bf16_hi(v.w) * w);
+      }
+    }
+    reinterpret_cast<uint4*>(out + (long long)r * cols)[c] = v;
+  }
+}
+
+// out[t, :] = sum_{j < top_k} (weights ? weights[t, j] : 1) * y[pos[t, j], :]   (fp32 sum, j ascending)
+__global__ void moe_combine_rows_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ pos,
+                                        const float* __restrict__ weights, __nv_bfloat16* __restrict__ out,
+                                        int tokens, int top_k, int cols) {
+  const int vec_per_row = cols >> 3;
+  const long long total = (long long)tokens * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const int t = (int)(i / vec_per_row), c = (int)(i - (long long)t * vec_per_row);
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    for (int j = 0; j < top_k; ++j) {
+      const int r = pos[t * top_k + j];
+      const float w = weights != nullptr ? weights[t * top_k + j] : 1.f;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(y + (long long)r * cols) + c);
+      acc[0] = fmaf(w, bf16_lo(v.x), acc[0]); acc[1] = fmaf(w, bf16_hi(v.x), acc[1]);
+      acc[2] = fmaf(w, bf16_lo(v.y), acc[2]); acc[3] = fmaf(w, bf16_hi(v.y), acc[3]);
+      acc[4] = fmaf(w, bf16_lo(v.z), acc[4]); acc[5] = fmaf(w, bf16_hi(v.z), acc[5]);
+      acc[6] = fmaf(w, bf16_lo(v.w), acc[6]); acc[7] = fmaf(w, bf16_hi(v.w), acc[7]);
+    }
+    reinterpret_cast<uint4*>(out + (long long)t * cols)[c] =
+        make_uint4(pack2(acc[0], acc[1]), pack2(acc[2], acc[3]), pack2(acc[4], acc[5]), pack2(acc[6], acc[7]));
+  }
+}
+
+// dots[t, j] = sum_c g[t, c] * y[pos[t, j], c]: the gradient of the routing weight of (token t, choice j).
+// One warp per (t, j); lanes stride the row 16 bytes at a time, partials added by a shuffle tree (fixed order).
+__global__ void moe_row_dot_kernel(const __nv_bfloat16* __restrict__ g, const __nv_bfloat16* __restrict__ y,
+                                   const int* __restrict__ pos, float* __restrict__ dots, int pairs, int top_k, int cols) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int p = blockIdx.x * warps_per_block + (threadIdx.x >> 5); p < pairs; p += gridDim.x * warps_per_block) {
+    const int t = p / top_k;
+    const uint4* gr = reinterpret_cast<const uint4*>(g + (long long)t * cols);
+    const uint4* yr = reinterpret_cast<const uint4*>(y + (long long)pos[p] * cols);
+    float acc = 0.f;
+    for (int c = lane; c < (cols >> 3); c += 32) {
+      const uint4 a = __ldg(gr + c), b = __ldg(yr + c);
+      acc = fmaf(bf16_lo(a.x), bf16_lo(b.x), acc); acc = fmaf(bf16_hi(a.x), bf16_hi(b.x), acc);
+      acc = fmaf(bf16_lo(a.y), bf16_lo(b.y), acc); acc = fmaf(bf16_hi(a.y), bf16_hi(b.y), acc);
+      acc = fmaf(bf16_lo(a.z), bf16_lo(b.z), acc); acc = fmaf(bf16_hi(a.z), bf16_hi(b.z), acc);
+      acc = fmaf(bf16_lo(a.w), bf16_lo(b.w), acc); acc = fmaf(bf16_hi(a.w), bf16_hi(b.w), acc);
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (lane == 0) dots[p] = acc;
+  }
+}
+
+// The gated activation on interleaved (gate, up) column pairs (modeling_gpt_oss.py:76-82):
+//   gate = min(g, limit), up = clamp(u, -limit, limit), h = (up + 1) * gate * sigmoid(alpha * gate).
+struct GluParts {
+  float gate, up, sig;
+};
+__device__ __forceinline__ GluParts glu_parts(float g, float u) {
+  GluParts p;
+  p.gate = fminf(g, kGluLimit);
+  p.up = fminf(fmaxf(u, -kGluLimit), kGluLimit);
+  p.sig = 1.f / (1.f + __expf(-kGluAlpha * p.gate));
+  return p;
+}
+__device__ __forceinline__ float glu_value(uint32_t gate_up) {
+  const GluParts p = glu_parts(bf16_lo(gate_up), bf16_hi(gate_up));
+  return (p.up + 1.f) * p.gate * p.sig;
+}
+
+// h[r, c] = glu(y1[r, 2c], y1[r, 2c + 1]); y1 has 2 * cols_h columns.  One thread: 16 input -> 8 output columns.
+__global__ void moe_glu_kernel(const __nv_bfloat16* __restrict__ y1, __nv_bfloat16* __restrict__ h, long long rows, int cols_h) {
+  const int vec_per_row = cols_h >> 3;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(y1) + 2 * i;   // (rows are 2 * cols_h wide: vector 2i, 2i+1 of the flat array)
+    const uint4 a = __ldg(src), b = __ldg(src + 1);
+    reinterpret_cast<uint4*>(h)[i] = make_uint4(pack2(glu_value(a.x), glu_value(a.y)), pack2(glu_value(a.z), glu_value(a.w)),
+                                                pack2(glu_value(b.x), glu_value(b.y)), pack2(glu_value(b.z), glu_value(b.w)));
+  }
+}
+
+// dy1[r, 2c], dy1[r, 2c + 1] from dh[r, c] and y1 (clamps pass the gradient inside their closed range, as torch.clamp does).
+__device__ __forceinline__ uint32_t glu_grad(uint32_t gate_up, float dh) {
+  const float g = bf16_lo(gate_up), u = bf16_hi(gate_up);
+  const GluParts p = glu_parts(g, u);
+  const float glu = p.gate * p.sig;
+  const float d_gate = g <= kGluLimit ? dh * (p.up + 1.f) * (p.sig + kGluAlpha * glu * (1.f - p.sig)) : 0.f;
+  const float d_up = (u >= -kGluLimit && u <= kGluLimit) ? dh * glu : 0.f;
+  return pack2(d_gate, d_up);
+}
+__global__ void moe_glu_bwd_kernel(const __nv_bfloat16* __restrict__ y1, const __nv_bfloat16* __restrict__ dh,
+                                   __nv_bfloat16* __restrict__ dy1, long long rows, int cols_h) {
+  const int vec_per_row = cols_h >> 3;
+  const long long total = rows * vec_per_row;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+    const uint4* src = reinterpret_cast<const uint4*>(y1) + 2 * i;
+    const uint4 a = __ldg(src), b = __ldg(src + 1);
+    const uint4 d = __ldg(reinterpret_cast<const uint4*>(dh) + i);
+    uint4* dst = reinterpret_cast<uint4*>(dy1) + 2 * i;
+    dst[0] = make_uint4(glu_grad(a.x, bf16_lo(d.x)), glu_grad(a.y, bf16_hi(d.x)), glu_grad(a.z, bf16_lo(d.y)), glu_grad(a.w, bf16_hi(d.y)));
+    dst[1] = make_uint4(glu_grad(b.x, bf16_lo(d.z)), glu_grad(b.y, bf16_hi(d.z)), glu_grad(b.z, bf16_lo(d.w)), glu_grad(b.w, bf16_hi(d.w)));
+  }
+}
+
+// db[g, c] = sum over the rows r of group g of dy[r, c] (fp32, rows ascending).  Block = (group, 512 columns):
+// a thread owns one column pair and walks the group's rows; a warp reads 128 contiguous bytes per row.
+__global__ void moe_bias_grad_kernel(const __nv_bfloat16* __restrict__ dy, const int* __restrict__ offsets,
+                                     __nv_bfloat16* __restrict__ db, int cols) {
+  const int g = blockIdx.y;
+  const int c2 = blockIdx.x * blockDim.x + threadIdx.x;   // column pair
+  if (2 * c2 >= cols) return;
+  const int r0 = offsets[g], r1 = offsets[g + 1];
+  float s0 = 0.f, s1 = 0.f;
+  const uint32_t* col = reinterpret_cast<const uint32_t*>(dy) + c2;
+  const long long stride = cols >> 1;
+  for (int r = r0; r < r1; ++r) {
+    const uint32_t w = __ldg(col + r * stride);
+    s0 += bf16_lo(w);
+    s1 += bf16_hi(w);
+  }
+  reinterpret_cast<uint32_t*>(db)[(long long)g * stride + c2] = pack2(s0, s1);
+}
+
+}  // namespace b200moe

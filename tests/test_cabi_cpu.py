@@ -18,9 +18,11 @@ def lib():
 
 
 def test_every_declared_symbol_is_exported(lib):
-    header = open(os.path.join(ROOT, "include", "b200attn.h")).read()
-    header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
-    declared = set(re.findall(r"\b(b200attn_[a-z_0-9]+)\s*\(", header))
+    declared = set()
+    for name in ("b200attn.h", "b200moe.h"):
+        header = open(os.path.join(ROOT, "include", name)).read()
+        header = re.sub(r"/\*.*?\*/", "", header, flags=re.S)
+        declared |= set(re.findall(r"\b(b200(?:attn|moe)_[a-z_0-9]+)\s*\(", header))
     assert declared == set(_cabi.EXPORTS)
     for name in declared:
         assert hasattr(lib, name), name
@@ -29,6 +31,25 @@ def test_every_declared_symbol_is_exported(lib):
 def test_struct_mirror_matches(lib):
     assert lib.b200attn_sizeof_params() == ctypes.sizeof(_cabi.Params)
     assert lib.b200attn_version() == 1
+
+
+def test_moe_struct_mirror_and_argument_validation(lib):
+    assert lib.b200moe_sizeof_gemm_params() == ctypes.sizeof(_cabi.MoeGemmParams)
+    assert lib.b200moe_grouped_gemm(None) == -1
+    buf = torch.zeros(1 << 12, dtype=torch.bfloat16)
+    off = torch.zeros(3, dtype=torch.int32)
+    p = _cabi.MoeGemmParams(op=_cabi.MOE_ROWS_NN, num_groups=2, rows=256, N=64, K=64, offsets=off.data_ptr(),
+                            a=buf.data_ptr(), b=buf.data_ptr(), d=buf.data_ptr(), device=0)
+    p.rows = 200
+    assert lib.b200moe_grouped_gemm(ctypes.byref(p)) == -2              # rows not a multiple of 128
+    p.rows, p.N = 256, 60
+    assert lib.b200moe_grouped_gemm(ctypes.byref(p)) == -4              # columns not a multiple of 8
+    p.N, p.op = 64, 7
+    assert lib.b200moe_grouped_gemm(ctypes.byref(p)) == -1              # unknown operation
+    p.op, p.num_groups = _cabi.MOE_ROWS_NN, 1000
+    assert lib.b200moe_grouped_gemm(ctypes.byref(p)) == -2              # too many groups
+    assert lib.b200moe_gather_rows(None, None, None, None, 1, 8, 0, None) == -1
+    assert lib.b200moe_glu(buf.data_ptr(), buf.data_ptr(), 4, 12, 0, None) == -4   # 12 columns: not a multiple of 8
 
 
 def test_helpers(lib):

@@ -1,0 +1,226 @@
+"""The mixture-of-experts path on the GPU, through the C ABI: the grouped GEMM in its three forms against
+fp32 matrix products, the memory-bound kernels against tensor expressions, and the whole block (forward and
+every gradient) against the fp32 oracle, the golden fixtures and the unmodified Hugging Face module."""
+import ctypes
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN_DIR
+from oracle.moe_fp32 import MOE_CASES, MoeCase, apply_gate, make_moe_inputs, moe_experts_fwd_bwd
+from oregon_gpt_oss_patching_b200 import _cabi
+from oregon_gpt_oss_patching_b200.attention_kernel import last_status
+from oregon_gpt_oss_patching_b200.moe_experts import (b200_experts_forward, grouped_gemm, moe_experts, patch_moe_experts,
+                                                      route, unpatch_moe_experts)
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+TOL = 2e-2   # bf16 operands and results, fp32 accumulation: max|a-b| / max|b| against fp32 on the same inputs
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).abs().max() / b.float().abs().max().clamp_min(1e-30))
+
+
+def _segments(counts):
+    """Padded offsets (multiples of 128) for the given rows per group, and the buffer size with slack behind them."""
+    off = [0]
+    for c in counts:
+        off.append(off[-1] + (c + 127) // 128 * 128)
+    return off, off[-1] + 256
+
+
+def _rand(*shape, scale=1.0, seed=0):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(torch.bfloat16).to(DEV)
+
+
+# rows per group: empty groups, half tiles (<= 128 rows), full + half (257..384), several full tiles
+GROUPS = [[300, 0, 128, 129, 1, 700], [64], [0, 0, 256], [513, 384]]
+
+
+@pytest.mark.parametrize("counts", GROUPS)
+@pytest.mark.parametrize("K,N", [(64, 192), (72, 200), (256, 64), (2880, 384)])
+def test_grouped_gemm_rows_nn_and_nt(counts, K, N):
+    off, rows = _segments(counts)
+    E = len(counts)
+    offsets = torch.tensor(off, dtype=torch.int32, device=DEV)
+    a = _rand(rows, K, seed=1)
+    w_nn = _rand(E, K, N, scale=K ** -0.5, seed=2)
+    bias = _rand(E, N, seed=3)
+    sentinel = 777.0
+    d = torch.full((rows, N), sentinel, dtype=torch.bfloat16, device=DEV)
+    grouped_gemm(_cabi.MOE_ROWS_NN, a, w_nn, d, offsets, bias=bias, N=N, K=K)
+    d_t = torch.full((rows, N), sentinel, dtype=torch.bfloat16, device=DEV)
+    w_nt = w_nn.transpose(1, 2).contiguous()          # (E, N, K): the same products from the transposed storage
+    grouped_gemm(_cabi.MOE_ROWS_NT, a, w_nt, d_t, offsets, N=N, K=K)
+    torch.cuda.synchronize()
+    for e in range(E):
+        seg = slice(off[e], off[e + 1])
+        if off[e] == off[e + 1]:
+            continue
+        ref = a[seg].float() @ w_nn[e].float()
+        assert rel(d[seg], ref + bias[e].float()) < TOL, ("nn", e)
+        assert rel(d_t[seg], ref) < TOL, ("nt", e)
+    # rows that belong to no group are not written
+    assert bool((d[off[-1]:] == sentinel).all()) and bool((d_t[off[-1]:] == sentinel).all())
+    assert last_status(DEV) == 0
+
+
+@pytest.mark.parametrize("counts", GROUPS)
+@pytest.mark.parametrize("M,N", [(64, 192), (200, 72), (384, 200), (2880, 192)])
+def test_grouped_gemm_inner_tn(counts, M, N):
+    off, rows = _segments(counts)
+    E = len(counts)
+    offsets = torch.tensor(off, dtype=torch.int32, device=DEV)
+    a = _rand(rows, M, seed=4)
+    b = _rand(rows, N, seed=5)
+    # padding rows hold zeros in the real buffers; here rows past a group's count are zeroed the same way
+    for e, c in enumerate(counts):
+        a[off[e] + c:off[e + 1]] = 0
+    d = torch.full((E, M, N), 777.0, dtype=torch.bfloat16, device=DEV)
+    grouped_gemm(_cabi.MOE_INNER_TN, a, b, d, offsets, M=M, N=N)
+    torch.cuda.synchronize()
+    for e in range(E):
+        seg = slice(off[e], off[e + 1])
+        ref = a[seg].float().T @ b[seg].float()
+        if off[e] == off[e + 1]:
+            assert float(d[e].abs().max()) == 0.0, e          # a group without rows: zeros, not garbage
+        else:
+            assert float((d[e].float() - ref).abs().max()) < TOL * max(1.0, float(ref.abs().max())), e
+    assert last_status(DEV) == 0
+
+
+def test_memory_bound_kernels_match_tensor_expressions():
+    lib = _cabi.load()
+    st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    T, k, E, H, I = 200, 4, 6, 136, 72
+    g = torch.Generator().manual_seed(7)
+    idx = torch.topk(torch.randn(T, E, generator=g), k, dim=-1).indices.to(DEV)
+    weights = torch.rand(T, k, generator=g).to(DEV)
+    r = route(idx, weights, E)
+    x = _rand(T, H, seed=8)
+    ptr = lambda t: None if t is None else ctypes.c_void_p(t.data_ptr())   # noqa: E731
+    # gather (with and without the per-row scale)
+    xs = torch.empty(r.rows, H, dtype=torch.bfloat16, device=DEV)
+    _cabi.check(lib.b200moe_gather_rows(ptr(x), ptr(r.row_token), None, ptr(xs), r.rows, H, 0, st), "gather")
+    valid = r.row_token >= 0
+    assert torch.equal(xs[valid], x[r.row_token[valid].long()]) and float(xs[~valid].abs().max()) == 0.0
+    xw = torch.empty_like(xs)
+    _cabi.check(lib.b200moe_gather_rows(ptr(x), ptr(r.row_token), ptr(r.row_weight), ptr(xw), r.rows, H, 0, st), "gather")
+    assert rel(xw[valid], x[r.row_token[valid].long()].float() * r.row_weight[valid, None]) < 4e-3
+    # combine: weighted and plain sums over a token's rows
+    y = _rand(r.rows, H, seed=9)
+    out = torch.empty(T, H, dtype=torch.bfloat16, device=DEV)
+    _cabi.check(lib.b200moe_combine_rows(ptr(y), ptr(r.pos), ptr(weights), ptr(out), T, k, H, 0, st), "combine")
+    ref = (y[r.pos.long()].float() * weights[..., None]).sum(1)
+    assert rel(out, ref) < 4e-3
+    _cabi.check(lib.b200moe_combine_rows(ptr(y), ptr(r.pos), None, ptr(out), T, k, H, 0, st), "combine")
+    assert rel(out, y[r.pos.long()].float().sum(1)) < 4e-3
+    # gradient of the routing weights
+    dots = torch.empty(T, k, dtype=torch.float32, device=DEV)
+    _cabi.check(lib.b200moe_row_dot(ptr(x), ptr(y), ptr(r.pos), ptr(dots), T, k, H, 0, st), "row_dot")
+    assert rel(dots, (x.float()[:, None, :] * y[r.pos.long()].float()).sum(-1)) < 1e-4
+    # gated activation and its derivative (values beyond both clamps included)
+    y1 = _rand(r.rows, 2 * I, scale=5.0, seed=10)
+    h = torch.empty(r.rows, I, dtype=torch.bfloat16, device=DEV)
+    _cabi.check(lib.b200moe_glu(ptr(y1), ptr(h), r.rows, I, 0, st), "glu")
+    y1f = y1.float().requires_grad_(True)
+    href = apply_gate(y1f)
+    assert rel(h, href) < 4e-3
+    dh = _rand(r.rows, I, seed=11)
+    dy1 = torch.empty_like(y1)
+    _cabi.check(lib.b200moe_glu_bwd(ptr(y1), ptr(dh), ptr(dy1), r.rows, I, 0, st), "glu_bwd")
+    href.backward(dh.float())
+    assert rel(dy1, y1f.grad) < 4e-3
+    # per-group column sums
+    db = torch.empty(E, 2 * I, dtype=torch.bfloat16, device=DEV)
+    _cabi.check(lib.b200moe_bias_grad(ptr(dy1), ptr(r.offsets), ptr(db), E, 2 * I, 0, st), "bias_grad")
+    off = r.offsets.tolist()
+    ref = torch.stack([dy1[off[e]:off[e + 1]].float().sum(0) for e in range(E)])
+    assert rel(db, ref) < 4e-3
+
+
+def _run_block(case, inputs=None):
+    hidden, idx, weights, w1, b1, w2, b2, dout = inputs or make_moe_inputs(case)
+    dev_in = [t.to(DEV) if t.dtype == torch.int64 else t.to(device=DEV, dtype=torch.bfloat16)
+              for t in (hidden, idx, weights, w1, b1, w2, b2, dout)]
+    h_, idx_, wt_, w1_, b1_, w2_, b2_, dout_ = dev_in
+    for t in (h_, wt_, w1_, b1_, w2_, b2_):
+        t.requires_grad_(True)
+    out = moe_experts(h_, idx_, wt_, w1_, b1_, w2_, b2_)
+    out.backward(dout_)
+    torch.cuda.synchronize()
+    return {"out": out.detach(), "dhidden": h_.grad, "dweights": wt_.grad, "dw1": w1_.grad, "db1": b1_.grad,
+            "dw2": w2_.grad, "db2": b2_.grad}
+
+
+@pytest.mark.parametrize("name", list(MOE_CASES))
+def test_block_matches_the_golden_fixtures(name):
+    z = np.load(os.path.join(GOLDEN_DIR, name + ".npz"))
+    got = _run_block(MOE_CASES[name])
+    for key, val in got.items():
+        assert rel(val.cpu(), torch.from_numpy(z[key])) < TOL, key
+    assert last_status(DEV) == 0
+
+
+@pytest.mark.parametrize("case", [
+    MoeCase("gptoss_dims", tokens=1024, hidden=2880, intermediate=2880, experts=8, top_k=4, seed=21),
+    MoeCase("many_experts", tokens=512, hidden=256, intermediate=384, experts=32, top_k=4, seed=22, unused_expert=5),
+    MoeCase("one_token", tokens=1, hidden=64, intermediate=64, experts=4, top_k=2, seed=23),
+], ids=lambda c: c.name)
+def test_block_matches_the_fp32_oracle(case):
+    inputs = make_moe_inputs(case)
+    ref = moe_experts_fwd_bwd(*[t.to(DEV) for t in inputs])
+    got = _run_block(case, inputs)
+    for key, val in got.items():
+        assert torch.isfinite(val.float()).all(), key
+        assert rel(val, ref[key]) < TOL, key
+    if case.unused_expert >= 0:
+        for key in ("dw1", "db1", "dw2", "db2"):
+            assert float(got[key][case.unused_expert].abs().max()) == 0.0
+    assert last_status(DEV) == 0
+
+
+def test_block_is_bitwise_deterministic():
+    case = MoeCase("det", tokens=700, hidden=192, intermediate=128, experts=8, top_k=4, seed=31)
+    a, b = _run_block(case), _run_block(case)
+    for key in a:
+        assert torch.equal(a[key], b[key]), key
+
+
+def test_patched_hugging_face_module_matches_the_unpatched_one():
+    from transformers.models.gpt_oss.configuration_gpt_oss import GptOssConfig
+    from transformers.models.gpt_oss.modeling_gpt_oss import GptOssMLP
+    cfg = GptOssConfig(hidden_size=128, intermediate_size=192, num_local_experts=8, num_experts_per_tok=4)
+    cfg._experts_implementation = "eager"
+    torch.manual_seed(0)
+    mlp = GptOssMLP(cfg).to(device=DEV, dtype=torch.bfloat16)
+    with torch.no_grad():
+        for p in mlp.parameters():
+            p.normal_(0.0, 0.05)
+    x = torch.randn(2, 96, 128, device=DEV, dtype=torch.bfloat16)
+
+    def run():
+        for p in mlp.parameters():
+            p.grad = None
+        xi = x.clone().requires_grad_(True)
+        y, scores = mlp(xi)
+        (y.float().pow(2).sum() + scores.float().sum()).backward()
+        return y.detach(), xi.grad, {n: p.grad.clone() for n, p in mlp.named_parameters()}
+
+    y0, dx0, g0 = run()
+    patch_moe_experts()
+    try:
+        y1, dx1, g1 = run()
+    finally:
+        unpatch_moe_experts()
+    # the unpatched module computes in bf16 throughout (bf16 matmul results, bf16 index_add_): both sides carry
+    # bf16 rounding, so the bar is looser than against fp32
+    assert rel(y1, y0) < 3e-2 and rel(dx1, dx0) < 3e-2
+    for n in g0:
+        assert rel(g1[n], g0[n]) < 5e-2, n
+    y2, _, _ = run()
+    assert torch.equal(y2, y0)   # un-patching restores the original forward
