@@ -169,7 +169,7 @@ def run_moe(args, rank, world, local_rank):
                         p_.grad = None
                     h_in.grad = None
                     w_in.grad = None
-                    mod(h_in, router_indices=idx, routing_weights=w_in).backward(dout)
+                    mod(h_in, idx, w_in).backward(dout)
 
                 ms = _time(hf_step, max(3, steps // 4), 2, stream)
                 contenders["hf_" + impl] = {"ms_per_step": round(ms, 3), "tflops": round(flops / (ms * 1e-3) / 1e12, 1),

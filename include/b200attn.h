@@ -189,6 +189,21 @@ int b200attn_bwd_dq(const b200attn_params* p);
 int b200attn_bwd_static_scratch(const b200attn_params* p);
 
 /*
+ * Rotary position embedding on a (batch, head, position, 64) view, one pass: out = rotate(x) with
+ * the half-split rotation of the attention layer the reference patches (the `apply_rotary_pos_emb`
+ * call in front of the patched function, transformers/models/gpt_oss/modeling_gpt_oss.py:226-242,
+ * :318-319): out[..., :32] = x[..., :32] * cos - x[..., 32:] * sin, out[..., 32:] = x[..., 32:] * cos +
+ * x[..., :32] * sin.  x and out may have any outer strides (the projection's (B,S,H,d) output is read
+ * where it lies, the result lands in the layout b200attn_fwd takes in place) and may be the same
+ * buffer.  cos_table / sin_table: bf16 (B, S, 32) with the given element strides (multiples of 8; a
+ * batch stride of 0 shares one table).  inverse != 0 rotates the other way: the gradient of the
+ * forward rotation, applied to dq / dk.
+ */
+int b200attn_rope(const b200attn_tensor* x, const b200attn_tensor* out, const void* cos_table, const void* sin_table,
+                  int64_t table_stride_b, int64_t table_stride_s, int32_t B, int32_t H, int32_t S, int32_t inverse,
+                  int32_t device, void* stream);
+
+/*
  * Self-test of the tensor-core building blocks, used by the test-suite: D = A * B^T for one
  * 128 x N x K tile through TMA + tcgen05.  No counterpart in the reference.
  *   mode 0: A (128 x K) and B (N x K) both K-contiguous in shared memory, K = 64, N = 128

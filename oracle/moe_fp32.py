@@ -74,26 +74,39 @@ def apply_gate(gate_up: torch.Tensor) -> torch.Tensor:
     return (up + 1) * glu
 
 
-def moe_experts_forward(hidden, idx, weights, w1, b1, w2, b2):
+def round_through(x: torch.Tensor, dtype) -> torch.Tensor:
+    """x rounded to `dtype` (back in x's own dtype) with the identity as its derivative."""
+    return x if dtype is None else x + (x.to(dtype).to(x.dtype) - x).detach()
+
+
+def moe_experts_forward(hidden, idx, weights, w1, b1, w2, b2, preact_dtype=None):
     """modeling_gpt_oss.py:84-114: the loop over the experts, with an out-of-place ``index_add`` so that autograd
-    can differentiate with respect to everything (fp32, so the order of the additions only moves the last bit)."""
+    can differentiate with respect to everything (fp32, so the order of the additions only moves the last bit).
+
+    ``preact_dtype``: where the module runs in bf16 its pre-activation ``gate_up`` IS a bf16 tensor, and the gate's
+    derivative is discontinuous at the clamps (7 and +-7): a value that fp32 puts at 7.01 and bf16 at 7.0 has its
+    gradient switched on.  With wide pre-activations a few such elements per token move the max-norm of
+    dhidden / dw1 by several per cent, whatever the implementation.  Passing ``torch.bfloat16`` rounds the
+    pre-activation at that one place (identity derivative), which is the fair reference for a bf16 pipeline;
+    the golden fixtures are plain fp32 (``None``)."""
     out = torch.zeros_like(hidden)
     for e in range(w1.shape[0]):
         token, choice = (idx == e).nonzero(as_tuple=True)                 # :103 `torch.where(expert_mask[e])`
         if token.numel() == 0:                                            # :93-97 only experts that were hit
             continue
         gate_up = hidden[token] @ w1[e] + b1[e]                           # :104-105
+        gate_up = round_through(gate_up, preact_dtype)
         gated = apply_gate(gate_up)                                       # :106
         y = gated @ w2[e] + b2[e]                                         # :107
         out = out.index_add(0, token, y * weights[token, choice, None])   # :108-109
     return out
 
 
-def moe_experts_fwd_bwd(hidden, idx, weights, w1, b1, w2, b2, dout):
+def moe_experts_fwd_bwd(hidden, idx, weights, w1, b1, w2, b2, dout, preact_dtype=None):
     """Output and the gradients of everything differentiable, in the dtype of the inputs."""
     leaves = [t.detach().clone().requires_grad_(True) for t in (hidden, weights, w1, b1, w2, b2)]
     h_, wt_, w1_, b1_, w2_, b2_ = leaves
-    out = moe_experts_forward(h_, idx, wt_, w1_, b1_, w2_, b2_)
+    out = moe_experts_forward(h_, idx, wt_, w1_, b1_, w2_, b2_, preact_dtype)
     out.backward(dout)
     return {"out": out.detach(), "dhidden": h_.grad, "dweights": wt_.grad, "dw1": w1_.grad, "db1": b1_.grad,
             "dw2": w2_.grad, "db2": b2_.grad}

@@ -17,7 +17,7 @@ EXPORTS = (
     "b200attn_version", "b200attn_sizeof_params", "b200attn_strerror", "b200attn_padded_len", "b200attn_dsinks_scratch_floats",
     "b200attn_fwd", "b200attn_bwd", "b200attn_bwd_preprocess", "b200attn_bwd_dsinks", "b200attn_bwd_dkdv",
     "b200attn_bwd_dq", "b200attn_bwd_dq_is_fused", "b200attn_bwd_static_scratch", "b200attn_umma_selftest",
-    "b200attn_wait_selftest",
+    "b200attn_wait_selftest", "b200attn_rope",
     "b200moe_sizeof_gemm_params", "b200moe_grouped_gemm", "b200moe_gather_rows", "b200moe_combine_rows", "b200moe_row_dot",
     "b200moe_glu", "b200moe_glu_bwd", "b200moe_bias_grad",
 )
@@ -106,6 +106,8 @@ def load() -> ctypes.CDLL:
         lib.b200attn_wait_selftest.restype = ctypes.c_int
         lib.b200attn_wait_selftest.argtypes = [ctypes.c_int64, ctypes.c_void_p, ctypes.c_int, ctypes.c_void_p]
         vp, i32, i64 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64
+        lib.b200attn_rope.restype = ctypes.c_int
+        lib.b200attn_rope.argtypes = [ctypes.POINTER(Tensor4), ctypes.POINTER(Tensor4), vp, vp, i64, i64, i32, i32, i32, i32, i32, vp]
         lib.b200moe_sizeof_gemm_params.restype = ctypes.c_size_t
         lib.b200moe_sizeof_gemm_params.argtypes = []
         if lib.b200moe_sizeof_gemm_params() != ctypes.sizeof(MoeGemmParams):

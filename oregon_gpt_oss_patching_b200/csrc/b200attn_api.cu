@@ -17,6 +17,7 @@
 #include "bwd_window_fused_kernel.cuh"
 #include "fwd_kernel.cuh"
 #include "fwd_packed_kernel.cuh"
+#include "rope_kernel.cuh"
 #include "umma_selftest.cuh"
 
 namespace {
@@ -380,6 +381,34 @@ int b200attn_wait_selftest(int64_t wait_limit_cycles, int32_t* status, int devic
   if ((rc = set_smem<umma_selftest_kernel>(smem))) return rc;
   umma_selftest_kernel<<<1, 128, smem, static_cast<cudaStream_t>(stream)>>>(unused, unused, 3, nullptr, nullptr, nullptr, status,
                                                                             (long long)wait_limit_cycles);
+  return launch_status();
+}
+
+int b200attn_rope(const b200attn_tensor* x, const b200attn_tensor* out, const void* cos_table, const void* sin_table,
+                  int64_t table_stride_b, int64_t table_stride_s, int32_t B, int32_t H, int32_t S, int32_t inverse,
+                  int32_t device, void* stream) {
+  if (x == nullptr || out == nullptr || cos_table == nullptr || sin_table == nullptr || B <= 0 || H <= 0 || S <= 0) return B200ATTN_EINVAL;
+  int rc;
+  if ((rc = check_tensor(*x, B, H, S)) || (rc = check_tensor(*out, B, H, S))) return rc;
+  if (!aligned16(cos_table) || !aligned16(sin_table) || table_stride_b % 8 || table_stride_s % 8 || table_stride_s < kHeadDim / 2)
+    return B200ATTN_EALIGN;
+  if ((rc = check_device(device))) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  RopeArgs a{};
+  a.x = strided(*x);
+  a.out = strided(*out);
+  a.cos = static_cast<const __nv_bfloat16*>(cos_table);
+  a.sin = static_cast<const __nv_bfloat16*>(sin_table);
+  a.cs_b = table_stride_b;
+  a.cs_s = table_stride_s;
+  a.B = B; a.H = H; a.S = S;
+  a.sin_sign = inverse ? -1.f : 1.f;
+  int sms = 148;
+  cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
+  const long long threads = (long long)B * H * S * 4;
+  const long long want = (threads + 255) / 256, cap = (long long)sms * 16;
+  rope_kernel<<<(int)(want < cap ? want : cap), 256, 0, static_cast<cudaStream_t>(stream)>>>(a);
   return launch_status();
 }
 

@@ -5,12 +5,13 @@ launched by ``scripts/run_full_sft.sh`` with ``configs/sft_full.yaml`` / ``confi
 the model is built from ``GptOssConfig`` with random bf16 weights (no checkpoint, no dataset:
 token ids are uniform over the vocabulary), attention is patched exactly as the reference does
 (``sft.py:18``), gradient checkpointing is on (``sft_full.yaml:13``), batch 1 per GPU and
-``max_length`` 8192 (``sft_full.yaml:16,18``).  Data parallelism is plain replication with a
+``max_length`` 8192 (``sft_full.yaml:16,18``); the expert block runs through this library's grouped GEMMs unless
+``--moe hf`` / ``--moe hf_eager`` asks for transformers' own implementations.  Data parallelism is plain replication with a
 bucketed NCCL all-reduce of the bf16 gradients (torch DDP) instead of DeepSpeed ZeRO-3, and the
 optimizer is state-free SGD, so that one replica (41.8 GB weights + 41.8 GB gradients for the 20b
 architecture) fits one 180 GB GPU.
 
-    python -m oregon_gpt_oss_patching_b200.sft_step [--layers 24] [--seq 8192] [--steps 3] [--unpatched]
+    python -m oregon_gpt_oss_patching_b200.sft_step [--layers 24] [--seq 8192] [--steps 3] [--unpatched] [--moe b200|hf|hf_eager]
     torchrun --nproc-per-node N -m oregon_gpt_oss_patching_b200.sft_step ...
 
 Prints one JSON line (rank 0): tokens/s/GPU, ms/step, peak memory.
@@ -25,12 +26,14 @@ import time
 import torch
 
 
-def build_model(layers: int, experts: int, vocab: int, device, seed: int = 0):
+def build_model(layers: int, experts: int, vocab: int, device, seed: int = 0, experts_implementation=None):
     from transformers import GptOssConfig, GptOssForCausalLM
     cfg = GptOssConfig(num_hidden_layers=layers, num_local_experts=experts, vocab_size=vocab,
                        layer_types=["sliding_attention" if i % 2 == 0 else "full_attention" for i in range(layers)],
                        attention_dropout=0.0, use_cache=False)
     cfg._attn_implementation = "eager"   # the patch point is the eager function (patching.py:6-7 of the reference)
+    if experts_implementation is not None:
+        cfg._experts_implementation = experts_implementation
     torch.manual_seed(seed)
     prev = torch.get_default_dtype()
     torch.set_default_dtype(torch.bfloat16)
@@ -57,6 +60,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=1)
     ap.add_argument("--lr", type=float, default=1e-5)
     ap.add_argument("--unpatched", action="store_true", help="HF eager attention instead of the B200 kernels")
+    ap.add_argument("--moe", default="b200", choices=["b200", "hf", "hf_eager"],
+                    help="expert block: this library's grouped GEMMs, transformers' default (torch._grouped_mm where it "
+                         "can dispatch), or transformers' per-expert loop")
+    ap.add_argument("--hf-rope", action="store_true", help="keep transformers' rotary embedding (default: the one-pass kernel, "
+                    "whenever the attention is patched)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -70,8 +78,15 @@ def main():
     from . import patching
     if not args.unpatched:
         patching.patch_flash_attention()
+        if not args.hf_rope:
+            from . import rope
+            rope.patch_rotary_embedding()
 
-    model, cfg = build_model(args.layers, args.experts, args.vocab, dev)
+    from . import moe_experts
+    if args.moe == "b200":
+        moe_experts.patch_moe_experts()
+
+    model, cfg = build_model(args.layers, args.experts, args.vocab, dev, experts_implementation="eager" if args.moe == "hf_eager" else None)
     n_params = sum(p.numel() for p in model.parameters())
     net = model
     if world > 1:
@@ -106,14 +121,16 @@ def main():
     if world > 1:
         torch.distributed.all_reduce(ms, op=torch.distributed.ReduceOp.MAX)
     status = 0
-    if not args.unpatched:
+    if not args.unpatched or args.moe == "b200":
         from .attention_kernel import last_status
         status = int(last_status(dev))
     if rank == 0:
         print(json.dumps({
             "metric": "sft_tokens_per_s_per_gpu", "value": round(args.seq / (ms.item() * 1e-3), 1), "unit": "tokens/s/GPU",
             "n_gpus": world, "ms_per_step": round(ms.item(), 1), "steps": args.steps, "warmup": args.warmup,
-            "attention": "hf_eager" if args.unpatched else "b200", "loss": round(float(loss), 4), "kernel_status": status,
+            "attention": "hf_eager" if args.unpatched else "b200",
+            "rope": "hf" if (args.unpatched or args.hf_rope) else "b200",
+            "moe": args.moe if args.moe != "hf" else "hf:" + str(getattr(cfg, "_experts_implementation", None)), "loss": round(float(loss), 4), "kernel_status": status,
             "config": {"layers": args.layers, "experts": args.experts, "vocab": args.vocab, "seq_len": args.seq,
                        "params_b": round(n_params / 1e9, 2), "batch_per_gpu": 1, "grad_checkpointing": True,
                        "optimizer": "sgd (state-free)", "dp": "replicas + NCCL all-reduce (DDP)" if world > 1 else "none"},

@@ -31,13 +31,14 @@ def _run(extra):
 
 def test_one_fine_tuning_step_patched_and_unpatched_agree():
     patched = _run([])
-    eager = _run(["--unpatched"])
+    eager = _run(["--unpatched", "--moe", "hf_eager"])
     assert patched["attention"] == "b200" and eager["attention"] == "hf_eager"
+    assert patched["moe"] == "b200" and eager["moe"] == "hf_eager"
     assert patched["kernel_status"] == 0
     for rec in (patched, eager):
         assert rec["n_gpus"] == 1 and rec["config"]["seq_len"] == 512 and rec["config"]["layers"] == 2
         assert rec["value"] > 0 and rec["loss"] == rec["loss"]          # finite
-    # same weights (seeded), same batch, two SGD updates each: the losses differ by bf16 attention rounding only
+    # same weights (seeded), same batch, two SGD updates each: the losses differ by bf16 rounding in attention and the expert block only
     assert abs(patched["loss"] - eager["loss"]) < 2e-2 * abs(eager["loss"]), (patched["loss"], eager["loss"])
     # the patched step never materialises the S x S score matrix
     assert patched["peak_mem_gb"] <= eager["peak_mem_gb"] + 0.05

@@ -7,7 +7,7 @@ import pytest
 import torch
 
 from conftest import GOLDEN_DIR
-from oracle.moe_fp32 import MOE_CASES, apply_gate, make_moe_inputs, moe_experts_fwd_bwd
+from oracle.moe_fp32 import MOE_CASES, MoeCase, apply_gate, make_moe_inputs, moe_experts_fwd_bwd
 from oregon_gpt_oss_patching_b200.moe_experts import padded_rows, route
 
 TOL = 2e-6   # fp32 restatement vs fp32 module: summation-order differences only
@@ -65,3 +65,15 @@ def test_routing_bookkeeping(tokens, top_k, experts):
             assert off[e] <= row < off[e + 1] and int(r.row_token[row]) == t
             assert float(r.row_weight[row]) == float(weights[t, j])
     assert float(r.row_weight.sum()) == pytest.approx(float(weights.sum()), rel=1e-5)
+
+
+def test_rounding_the_preactivation_moves_gradients_at_the_clamps():
+    """Why the GPU tests at model-like widths compare with ``preact_dtype=torch.bfloat16``: rounding that one tensor
+    leaves the output within bf16 precision but switches gradient elements next to the clamps on or off."""
+    case = MoeCase("wide", tokens=256, hidden=128, intermediate=192, experts=8, top_k=4, seed=5)
+    inputs = make_moe_inputs(case)
+    plain = moe_experts_fwd_bwd(*inputs)
+    rounded = moe_experts_fwd_bwd(*inputs, preact_dtype=torch.bfloat16)
+    err = {k: float((rounded[k] - plain[k]).abs().max() / plain[k].abs().max()) for k in plain}
+    assert err["out"] < 1e-2 and err["dw2"] < 1e-2
+    assert err["dw1"] > 2e-2          # far beyond rounding noise: whole elements flipped
