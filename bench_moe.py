@@ -87,15 +87,6 @@ def run_moe(args, rank, world, local_rank):
     pairs = tokens * TOPK
     flops = block_flops(pairs)
 
-    leaves = [t.clone().requires_grad_(True) for t in (hidden, weights, w1, b1, w2, b2)]
-
-    def step():
-        for t in leaves:
-            t.grad = None
-        out = me.moe_experts(leaves[0], idx, leaves[1], leaves[2], leaves[3], leaves[4], leaves[5])
-        out.backward(dout)
-        return out
-
     # ---- the six grouped GEMMs alone, for the roofline of the dominant kernel ----
     r = me.route(idx, weights, E)
     rows = r.rows
@@ -120,6 +111,15 @@ def run_moe(args, rank, world, local_rank):
         torch.cuda.synchronize()
         print(json.dumps({"capture": "moe", "passes": args.warmup + args.steps}))
         return
+
+    leaves = [t.clone().requires_grad_(True) for t in (hidden, weights, w1, b1, w2, b2)]
+
+    def step():
+        for t in leaves:
+            t.grad = None
+        out = me.moe_experts(leaves[0], idx, leaves[1], leaves[2], leaves[3], leaves[4], leaves[5])
+        out.backward(dout)
+        return out
 
     steps, warm = args.steps, max(args.warmup, 3)
     sampler = ClockSampler(local_rank)

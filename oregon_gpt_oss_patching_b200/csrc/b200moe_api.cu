@@ -14,18 +14,30 @@ namespace {
 using namespace b200moe;
 using namespace b200attn::host;
 
-// 3-D bf16 map (inner, rows, groups) with the 128-byte swizzle; the inner box extent is always 64 elements.
-int make_map3(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+// 4-D bf16 maps with the 128-byte swizzle; the inner box extent is always 64 elements.
+int encode4(CUtensorMap* map, const void* ptr, const cuuint64_t (&dims)[4], const cuuint64_t (&strides)[3], const cuuint32_t (&box)[4]) {
   EncodeTiledFn fn = encode_tiled_fn();
   if (fn == nullptr) return B200ATTN_ECUDA;
-  cuuint64_t dims[3] = {inner, rows, groups};
-  cuuint64_t strides[2] = {inner * 2, inner * rows * 2};
-  cuuint32_t box[3] = {64, box_rows, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? B200ATTN_OK : B200ATTN_ETENSORMAP;
+}
+// (groups, rows, inner) row-major seen as (inner, rows, groups, 1): boxes of 64 inner elements x box_rows rows.
+int make_map_rows(CUtensorMap* map, const void* ptr, uint64_t inner, uint64_t rows, uint64_t groups, uint32_t box_rows) {
+  const cuuint64_t dims[4] = {inner, rows, groups, 1};
+  const cuuint64_t strides[3] = {inner * 2, inner * rows * 2, inner * rows * groups * 2};
+  const cuuint32_t box[4] = {64, box_rows, 1, 1};
+  return encode4(map, ptr, dims, strides, box);
+}
+// The same matrix with a width that is a multiple of 64, seen as (64, rows, width / 64, groups): one box of
+// (64, 64 rows, panels) lands `panels` neighbouring 64-column panels, each as a contiguous (64 rows x 128 B) tile.
+int make_map_panels(CUtensorMap* map, const void* ptr, uint64_t width, uint64_t rows, uint64_t groups, uint32_t panels) {
+  const cuuint64_t dims[4] = {64, rows, width / 64, groups};
+  const cuuint64_t strides[3] = {width * 2, 128, width * rows * 2};
+  const cuuint32_t box[4] = {64, 64, panels, 1};
+  return encode4(map, ptr, dims, strides, box);
 }
 
 int sm_count(int device) {
@@ -81,20 +93,25 @@ int b200moe_grouped_gemm(const b200moe_gemm_params* p) {
   if (!inner) {
     a.a_mn = 0;
     a.b_mn = p->op == B200MOE_ROWS_NN ? 1 : 0;
-    if ((rc = make_map3(&ta, p->a, p->K, p->rows, 1, kHalfM))) return rc;                        // (64 inner x 128 rows) boxes
-    if (a.b_mn) {
-      if ((rc = make_map3(&tb, p->b, p->N, p->K, p->num_groups, 64))) return rc;                 // (64 columns x 64 inner rows) panels
+    a.b_merged = (a.b_mn && p->N % 64 == 0) ? 1 : 0;
+    if ((rc = make_map_rows(&ta, p->a, p->K, p->rows, 1, kHalfM))) return rc;                    // (64 inner x 128 rows) boxes
+    if (a.b_merged) {
+      if ((rc = make_map_panels(&tb, p->b, p->N, p->K, p->num_groups, kBN / 64))) return rc;     // three (64 columns x 64 inner rows) panels per box
+    } else if (a.b_mn) {
+      if ((rc = make_map_rows(&tb, p->b, p->N, p->K, p->num_groups, 64))) return rc;             // one panel per box
     } else {
-      if ((rc = make_map3(&tb, p->b, p->K, p->N, p->num_groups, kBN))) return rc;                // (64 inner x 192 rows) boxes
+      if ((rc = make_map_rows(&tb, p->b, p->K, p->N, p->num_groups, kBN))) return rc;            // (64 inner x 192 rows) boxes
     }
-    if ((rc = make_map3(&td, p->d, p->N, p->rows, 1, kHalfM))) return rc;
+    if ((rc = make_map_rows(&td, p->d, p->N, p->rows, 1, kHalfM))) return rc;
     max_tiles = ((long long)p->rows / kHalfM + p->num_groups) * n_tiles;   // an upper bound; the kernel counts the real ones
   } else {
     a.a_mn = 1;
     a.b_mn = 1;
-    if ((rc = make_map3(&ta, p->a, p->M, p->rows, 1, 64))) return rc;
-    if ((rc = make_map3(&tb, p->b, p->N, p->rows, 1, 64))) return rc;
-    if ((rc = make_map3(&td, p->d, p->N, p->M, p->num_groups, kHalfM))) return rc;
+    a.a_merged = p->M % 64 == 0 ? 1 : 0;
+    a.b_merged = p->N % 64 == 0 ? 1 : 0;
+    if ((rc = a.a_merged ? make_map_panels(&ta, p->a, p->M, p->rows, 1, kBM / 64) : make_map_rows(&ta, p->a, p->M, p->rows, 1, 64))) return rc;
+    if ((rc = a.b_merged ? make_map_panels(&tb, p->b, p->N, p->rows, 1, kBN / 64) : make_map_rows(&tb, p->b, p->N, p->rows, 1, 64))) return rc;
+    if ((rc = make_map_rows(&td, p->d, p->N, p->M, p->num_groups, kHalfM))) return rc;
     max_tiles = (long long)p->num_groups * ((p->M + kBM - 1) / kBM) * n_tiles;
   }
   const size_t smem = sizeof(GemmSmem) + 1024;
@@ -179,8 +196,8 @@ int b200moe_bias_grad(const void* dy, const int32_t* offsets, void* db, int32_t 
   if ((rc = check_matrix(dy, cols)) || (rc = check_matrix(db, cols)) || (rc = check_device(device))) return rc;
   DeviceGuard guard(device);
   if (!guard.ok) return B200ATTN_ECUDA;
-  const dim3 grid((cols / 2 + 255) / 256, num_groups);
-  moe_bias_grad_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(dy), offsets,
+  const dim3 grid((cols + 255) / 256, num_groups);
+  moe_bias_grad_kernel<<<grid, kBiasGradWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(dy), offsets,
                                                                              static_cast<__nv_bfloat16*>(db), cols);
   return launch_status();
 }

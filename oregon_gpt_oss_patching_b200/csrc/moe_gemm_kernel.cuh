@@ -66,6 +66,7 @@ struct GemmSmem {
 struct GemmArgs {
   int mode;           // 0: rows grouped, 1: inner dimension grouped
   int a_mn, b_mn;     // operand forms: 0 = inner dimension contiguous, 1 = M/N contiguous
+  int a_merged, b_merged;   // an M/N-contiguous operand whose panels of a block arrive in one TMA box (width % 64 == 0)
   int num_groups;
   int M, N, K;        // mode 0: N output columns, K inner (M unused: rows come from offsets); mode 1: M x N per group (K unused)
   const int* offsets; // (num_groups + 1) row offsets of the groups, multiples of 128
@@ -82,19 +83,6 @@ struct GemmTile {
   int k_row0;    // mode 1: first row of the group (inner dimension origin)
   int k_blocks;  // inner blocks of 64
 };
-
-__device__ __forceinline__ void tma_load_3d(uint32_t dst_smem, const void* tmap, uint32_t bar, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst_smem), "l"(tmap), "r"(bar), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_3d(const void* tmap, uint32_t src_smem, int c0, int c1, int c2) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.global.shared::cta.bulk_group [%0, {%2, %3, %4}], [%1];"
-      ::"l"(tmap), "r"(src_smem), "r"(c0), "r"(c1), "r"(c2)
-      : "memory");
-}
 
 // Named barrier `id` among 128 threads, returning the OR of their predicates.
 __device__ __forceinline__ bool wg_barrier_or(int id, bool pred) {
@@ -197,11 +185,19 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
   tc_fence_after_sync();
   const uint32_t tmem = sm->tmem_base;
 
+  // Registers move from the warpgroup of the single-thread roles to the two epilogue warpgroups, which hold a
+  // whole packed accumulator row (96 registers) while they store it: 128 * 72 + 2 * 128 * 216 = 384 * 168.
+  if (warp < 4) {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
   if (warp == 0) {
     // ------------------------------------ TMA loader ------------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_a);
       prefetch_tmap(&tm_b);
+      // As few TMA operations per block as the layouts allow (the engine's issue rate, not its bandwidth, is what a
+      // block of seven 8 KB boxes ran into): M/N-contiguous operands whose width is a multiple of 64 are described
+      // to the engine as (64, rows, width/64) so that ONE box {64, 64 inner rows, panels} lands all the 64-element
+      // panels of a block, each panel a contiguous 8 KB tile as the MMA descriptors expect.
       TileWalker w(a, sm);
       GemmTile t;
       int it = 0;
@@ -211,24 +207,33 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           const int s = it % kGemmStages;
           if (it >= kGemmStages && !(ok = mbar_wait(smem_u32(&sm->bar_empty[s]), ((it / kGemmStages) - 1) & 1, abort_flag))) break;
           const uint32_t bar = smem_u32(&sm->bar_full[s]);
-          mbar_arrive_expect_tx(bar, t.halves * kHalfABytes + kBBytes);
           const uint32_t sa = smem_u32(sm->a[s]), sb = smem_u32(sm->b[s]);
           const int k0 = kb * kBK;
+          const int a_bytes = (a.a_merged ? 2 : t.halves) * kHalfABytes;   // a merged box always carries both halves
+          mbar_arrive_expect_tx(bar, a_bytes + kBBytes);
           if (a.mode == 0) {
             // A: rows x K, K contiguous: one (64 x 128-row) box per accumulator half
-            for (int h = 0; h < t.halves; ++h) tma_load_3d(sa + h * kHalfABytes, &tm_a, bar, k0, t.row0 + h * kHalfM, 0);
-            if (a.b_mn) {
-              // B_g: K x N, N contiguous: three (64 columns x 64 inner rows) panels
-              for (int p = 0; p < kBN / 64; ++p) tma_load_3d(sb + p * kPanelBytes, &tm_b, bar, t.n0 + p * 64, k0, t.g);
+            for (int h = 0; h < t.halves; ++h) tma_load_4d(sa + h * kHalfABytes, &tm_a, bar, k0, t.row0 + h * kHalfM, 0, 0);
+            if (!a.b_mn) {
+              tma_load_4d(sb, &tm_b, bar, k0, t.n0, t.g, 0);                       // B_g: N x K, K contiguous: one (64 x 192-row) box
+            } else if (a.b_merged) {
+              tma_load_4d(sb, &tm_b, bar, 0, k0, t.n0 >> 6, t.g);                  // B_g: K x N, N contiguous: three panels in one box
             } else {
-              // B_g: N x K, K contiguous: one (64 x 192-row) box
-              tma_load_3d(sb, &tm_b, bar, k0, t.n0, t.g);
+              for (int p = 0; p < kBN / 64; ++p) tma_load_4d(sb + p * kPanelBytes, &tm_b, bar, t.n0 + p * 64, k0, t.g, 0);
             }
           } else {
             // both operands rows x (M | N), read with the group's rows as the inner dimension
             const int r0 = t.k_row0 + k0;
-            for (int p = 0; p < 2 * t.halves; ++p) tma_load_3d(sa + p * kPanelBytes, &tm_a, bar, t.row0 + p * 64, r0, 0);
-            for (int p = 0; p < kBN / 64; ++p) tma_load_3d(sb + p * kPanelBytes, &tm_b, bar, t.n0 + p * 64, r0, 0);
+            if (a.a_merged) {
+              tma_load_4d(sa, &tm_a, bar, 0, r0, t.row0 >> 6, 0);                  // four panels (panels past M arrive as zeros)
+            } else {
+              for (int p = 0; p < 2 * t.halves; ++p) tma_load_4d(sa + p * kPanelBytes, &tm_a, bar, t.row0 + p * 64, r0, 0, 0);
+            }
+            if (a.b_merged) {
+              tma_load_4d(sb, &tm_b, bar, 0, r0, t.n0 >> 6, 0);
+            } else {
+              for (int p = 0; p < kBN / 64; ++p) tma_load_4d(sb + p * kPanelBytes, &tm_b, bar, t.n0 + p * 64, r0, 0, 0);
+            }
           }
           *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
         }
@@ -273,7 +278,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
       if (!ok && a.status != nullptr) atomicOr(a.status, 1);
     }
     __syncwarp();
-  } else if (warp >= 4) {
+  }
+  } else {
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
     // ------------------------------------- epilogue -------------------------------------
     const int wg = (warp - 4) >> 2;                               // accumulator half
     const int r = (warp & 3) * 32 + lane;                         // row of the half = tensor-memory lane
@@ -299,66 +306,72 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
         continue;
       }
       const int n_chunks = min(kBN / 64, (a.N - t.n0 + 63) / 64);
-      for (int c = 0; c < n_chunks; ++c) {
-        uint32_t v0[32], v1[32];
-        if (t.k_blocks > 0 && !failed) {
-          tmem_ld32(tmem_row + c * 64, v0);
-          tmem_ld32(tmem_row + c * 64 + 32, v1);
-          tmem_wait_ld();
-        } else {
+      // Phase 1, on the critical path of the next tile: the accumulator leaves tensor memory (+ bias, packed to
+      // bf16: 32 registers per 64 columns) and the MMAs of the next tile are released.  Phase 2, under those MMAs:
+      // the packed rows go through the staging tile to global memory.
+      uint32_t pk[kBN / 64][32];
 #pragma unroll
-          for (int e = 0; e < 32; ++e) v0[e] = v1[e] = 0u;   // a group without rows: D_g = 0
-        }
-        if (c == n_chunks - 1) {
-          tc_fence_before_sync();
-          mbar_arrive(bar_acc_empty);   // the accumulators are in registers: the next tile's MMAs may start
-        }
-        if (a.bias != nullptr) {
-          const __nv_bfloat16* bias = a.bias + (long long)t.g * a.N + t.n0 + c * 64;
-          const int valid = a.N - (t.n0 + c * 64);
-          if (valid >= 64) {   // (N is a multiple of 8 and the chunk starts at a multiple of 64: 16-byte aligned)
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 b0 = __ldg(reinterpret_cast<const uint4*>(bias) + q);
-              const uint4 b1 = __ldg(reinterpret_cast<const uint4*>(bias) + 4 + q);
-              const uint32_t w0[4] = {b0.x, b0.y, b0.z, b0.w}, w1[4] = {b1.x, b1.y, b1.z, b1.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {   // a bf16 is the upper half of the fp32 with the same value
-                v0[q * 8 + 2 * e] = __float_as_uint(__uint_as_float(v0[q * 8 + 2 * e]) + __uint_as_float(w0[e] << 16));
-                v0[q * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(v0[q * 8 + 2 * e + 1]) + __uint_as_float(w0[e] & 0xffff0000u));
-                v1[q * 8 + 2 * e] = __float_as_uint(__uint_as_float(v1[q * 8 + 2 * e]) + __uint_as_float(w1[e] << 16));
-                v1[q * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(v1[q * 8 + 2 * e + 1]) + __uint_as_float(w1[e] & 0xffff0000u));
-              }
-            }
+      for (int c = 0; c < kBN / 64; ++c) {
+        if (c < n_chunks) {
+          uint32_t v0[32], v1[32];
+          if (t.k_blocks > 0 && !failed) {
+            tmem_ld32(tmem_row + c * 64, v0);
+            tmem_ld32(tmem_row + c * 64 + 32, v1);
+            tmem_wait_ld();
           } else {
 #pragma unroll
-            for (int e = 0; e < 32; ++e) {
-              if (e < valid) v0[e] = __float_as_uint(__uint_as_float(v0[e]) + __bfloat162float(bias[e]));
-              if (e + 32 < valid) v1[e] = __float_as_uint(__uint_as_float(v1[e]) + __bfloat162float(bias[e + 32]));
+            for (int e = 0; e < 32; ++e) v0[e] = v1[e] = 0u;   // a group without rows: D_g = 0
+          }
+          if (a.bias != nullptr) {
+            const __nv_bfloat16* bias = a.bias + (long long)t.g * a.N + t.n0 + c * 64;
+            const int valid = a.N - (t.n0 + c * 64);
+            if (valid >= 64) {   // (N is a multiple of 8 and the chunk starts at a multiple of 64: 16-byte aligned)
+#pragma unroll
+              for (int q = 0; q < 4; ++q) {
+                const uint4 b0 = __ldg(reinterpret_cast<const uint4*>(bias) + q);
+                const uint4 b1 = __ldg(reinterpret_cast<const uint4*>(bias) + 4 + q);
+                const uint32_t w0[4] = {b0.x, b0.y, b0.z, b0.w}, w1[4] = {b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {   // a bf16 is the upper half of the fp32 with the same value
+                  v0[q * 8 + 2 * e] = __float_as_uint(__uint_as_float(v0[q * 8 + 2 * e]) + __uint_as_float(w0[e] << 16));
+                  v0[q * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(v0[q * 8 + 2 * e + 1]) + __uint_as_float(w0[e] & 0xffff0000u));
+                  v1[q * 8 + 2 * e] = __float_as_uint(__uint_as_float(v1[q * 8 + 2 * e]) + __uint_as_float(w1[e] << 16));
+                  v1[q * 8 + 2 * e + 1] = __float_as_uint(__uint_as_float(v1[q * 8 + 2 * e + 1]) + __uint_as_float(w1[e] & 0xffff0000u));
+                }
+              }
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e) {
+                if (e < valid) v0[e] = __float_as_uint(__uint_as_float(v0[e]) + __bfloat162float(bias[e]));
+                if (e + 32 < valid) v1[e] = __float_as_uint(__uint_as_float(v1[e]) + __bfloat162float(bias[e + 32]));
+              }
             }
           }
-        }
-        // the previous store of this warpgroup must have read the staging tile
-        if (leader) tma_store_wait_read();
-        if (wg_barrier_or(1 + wg, failed)) { failed = true; break; }
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          *reinterpret_cast<uint4*>(out_row + ((q ^ (r & 7)) << 4)) =
-              make_uint4(pack_bf16(__uint_as_float(v0[q * 8]), __uint_as_float(v0[q * 8 + 1])),
-                         pack_bf16(__uint_as_float(v0[q * 8 + 2]), __uint_as_float(v0[q * 8 + 3])),
-                         pack_bf16(__uint_as_float(v0[q * 8 + 4]), __uint_as_float(v0[q * 8 + 5])),
-                         pack_bf16(__uint_as_float(v0[q * 8 + 6]), __uint_as_float(v0[q * 8 + 7])));
-          *reinterpret_cast<uint4*>(out_row + (((q + 4) ^ (r & 7)) << 4)) =
-              make_uint4(pack_bf16(__uint_as_float(v1[q * 8]), __uint_as_float(v1[q * 8 + 1])),
-                         pack_bf16(__uint_as_float(v1[q * 8 + 2]), __uint_as_float(v1[q * 8 + 3])),
-                         pack_bf16(__uint_as_float(v1[q * 8 + 4]), __uint_as_float(v1[q * 8 + 5])),
-                         pack_bf16(__uint_as_float(v1[q * 8 + 6]), __uint_as_float(v1[q * 8 + 7])));
+          for (int e = 0; e < 16; ++e) {
+            pk[c][e] = pack_bf16(__uint_as_float(v0[2 * e]), __uint_as_float(v0[2 * e + 1]));
+            pk[c][16 + e] = pack_bf16(__uint_as_float(v1[2 * e]), __uint_as_float(v1[2 * e + 1]));
+          }
         }
-        fence_proxy_async_smem();   // written with ordinary stores, read by the TMA engine
-        wg_barrier_or(1 + wg, false);
-        if (leader) {
-          tma_store_3d(&tm_d, smem_u32(sm->out[wg]), t.n0 + c * 64, t.row0 + wg * kHalfM, a.mode == 0 ? 0 : t.g);
-          tma_store_commit();
+      }
+      tc_fence_before_sync();
+      mbar_arrive(bar_acc_empty);   // the accumulators are in registers: the next tile's MMAs may start
+#pragma unroll
+      for (int c = 0; c < kBN / 64; ++c) {
+        if (c < n_chunks) {
+          // the previous store of this warpgroup must have read the staging tile
+          if (leader) tma_store_wait_read();
+          if (wg_barrier_or(1 + wg, failed)) { failed = true; break; }
+#pragma unroll
+          for (int q = 0; q < 8; ++q)   // 16-byte chunk q of row r sits at chunk position q ^ (r % 8)
+            *reinterpret_cast<uint4*>(out_row + ((q ^ (r & 7)) << 4)) =
+                make_uint4(pk[c][q * 4], pk[c][q * 4 + 1], pk[c][q * 4 + 2], pk[c][q * 4 + 3]);
+          fence_proxy_async_smem();   // written with ordinary stores, read by the TMA engine
+          wg_barrier_or(1 + wg, false);
+          if (leader) {
+            tma_store_4d(&tm_d, smem_u32(sm->out[wg]), t.n0 + c * 64, t.row0 + wg * kHalfM, a.mode == 0 ? 0 : t.g, 0);
+            tma_store_commit();
+          }
         }
       }
       if (failed) { ok = false; break; }

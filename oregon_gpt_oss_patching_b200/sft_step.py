@@ -63,6 +63,8 @@ def main():
     ap.add_argument("--moe", default="b200", choices=["b200", "hf", "hf_eager"],
                     help="expert block: this library's grouped GEMMs, transformers' default (torch._grouped_mm where it "
                          "can dispatch), or transformers' per-expert loop")
+    ap.add_argument("--no-allreduce", action="store_true", help="attribution run: data-parallel replicas that skip the gradient "
+                    "all-reduce (the difference to a normal run is the part of the all-reduce that backward does not hide)")
     ap.add_argument("--hf-rope", action="store_true", help="keep transformers' rotary embedding (default: the one-pass kernel, "
                     "whenever the attention is patched)")
     args = ap.parse_args()
@@ -89,7 +91,7 @@ def main():
     model, cfg = build_model(args.layers, args.experts, args.vocab, dev, experts_implementation="eager" if args.moe == "hf_eager" else None)
     n_params = sum(p.numel() for p in model.parameters())
     net = model
-    if world > 1:
+    if world > 1 and not args.no_allreduce:
         net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[local_rank], gradient_as_bucket_view=True,
                                                         bucket_cap_mb=512, static_graph=True)
     g = torch.Generator().manual_seed(rank)
@@ -133,7 +135,7 @@ def main():
             "moe": args.moe if args.moe != "hf" else "hf:" + str(getattr(cfg, "_experts_implementation", None)), "loss": round(float(loss), 4), "kernel_status": status,
             "config": {"layers": args.layers, "experts": args.experts, "vocab": args.vocab, "seq_len": args.seq,
                        "params_b": round(n_params / 1e9, 2), "batch_per_gpu": 1, "grad_checkpointing": True,
-                       "optimizer": "sgd (state-free)", "dp": "replicas + NCCL all-reduce (DDP)" if world > 1 else "none"},
+                       "optimizer": "sgd (state-free)", "dp": ("replicas, all-reduce skipped (attribution run)" if args.no_allreduce else "replicas + NCCL all-reduce (DDP)") if world > 1 else "none"},
             "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2**30, 1), "data": "synthetic",
             "wall_s": round(time.perf_counter() - t0, 1)}), flush=True)
     if world > 1:
