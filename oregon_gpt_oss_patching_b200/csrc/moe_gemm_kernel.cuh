@@ -22,10 +22,12 @@
 // Persistent: CTA c takes tiles c, c + gridDim.x, ...; consecutive tiles share the A rows (mode 0) and walk the
 // columns of one expert's weights, so an expert's weights are read from HBM once and then hit in L2.
 //
-// Warp 0 lane 0: every TMA load.  Warp 1 lane 0: every MMA (warp 1 owns the tensor memory).  Warps 4-7 /
-// 8-11: epilogue of accumulator rows 0-127 / 128-255: tensor memory -> (+ bias) -> bf16 -> shared memory
-// (swizzled 128 x 64 tile) -> one TMA store per 64 columns; rows or columns past the end of D are clipped by
-// the store.  Every wait is bounded.
+// Warp 0 lane 0: every TMA load (two or three operations per inner block: an M/N-contiguous operand whose width
+// is a multiple of 64 is described to the engine as (64, rows, width / 64), so one box lands all its 64-element
+// panels).  Warp 1 lane 0: every MMA (warp 1 owns the tensor memory).  Warps 4-7 / 8-11: epilogue of
+// accumulator rows 0-127 / 128-255 in two phases: tensor memory -> (+ bias) -> packed bf16 in registers, which
+// releases the accumulators to the next tile's MMAs; then registers -> shared memory (swizzled 128 x 64 tile) ->
+// one TMA store per 64 columns; rows or columns past the end of D are clipped by the store.  Every wait is bounded.
 #pragma once
 #include <cuda.h>
 

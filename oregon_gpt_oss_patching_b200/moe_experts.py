@@ -139,7 +139,6 @@ class _moe_experts(torch.autograd.Function):
         _cabi.check(lib.b200moe_combine_rows(_ptr(y2), _ptr(r.pos), _ptr(weights), _ptr(out), T, k, H, di, st), "b200moe_combine_rows")
         ctx.save_for_backward(xs, y1, h, y2, w1, w2, r.offsets, r.row_token, r.pos, r.row_weight)
         ctx.weights_dtype = routing_weights.dtype
-        ctx.mark_non_differentiable(router_indices)
         return out
 
     @staticmethod
