@@ -51,6 +51,9 @@ typedef struct b200moe_gemm_params {
   int32_t device;
   void* stream;           /* cudaStream_t */
   int32_t* status;        /* device int32, may be NULL */
+  int32_t max_ctas;       /* 0: one persistent CTA per SM.  > 0: at most this many, for callers that run another
+                             kernel beside it (a collective's CTAs hold SMs, and a persistent CTA without an SM
+                             waits for one to finish all of its tiles) */
 } b200moe_gemm_params;
 
 /* sizeof(b200moe_gemm_params) as compiled, for bindings that mirror the struct. */

@@ -87,14 +87,15 @@ int b200moe_grouped_gemm(const b200moe_gemm_params* p) {
   a.offsets = p->offsets;
   a.bias = static_cast<const __nv_bfloat16*>(p->bias);
   a.status = p->status;
-  CUtensorMap ta, tb, td;
+  CUtensorMap ta, ta_full, tb, td;
   long long max_tiles;
   const long long n_tiles = (p->N + kBN - 1) / kBN;
   if (!inner) {
     a.a_mn = 0;
     a.b_mn = p->op == B200MOE_ROWS_NN ? 1 : 0;
     a.b_merged = (a.b_mn && p->N % 64 == 0) ? 1 : 0;
-    if ((rc = make_map_rows(&ta, p->a, p->K, p->rows, 1, kHalfM))) return rc;                    // (64 inner x 128 rows) boxes
+    if ((rc = make_map_rows(&ta, p->a, p->K, p->rows, 1, kHalfM))) return rc;                    // (64 inner x 128 rows) boxes: half tiles
+    if ((rc = make_map_rows(&ta_full, p->a, p->K, p->rows, 1, kBM))) return rc;                  // (64 inner x 256 rows) boxes: full tiles
     if (a.b_merged) {
       if ((rc = make_map_panels(&tb, p->b, p->N, p->K, p->num_groups, kBN / 64))) return rc;     // three (64 columns x 64 inner rows) panels per box
     } else if (a.b_mn) {
@@ -112,13 +113,16 @@ int b200moe_grouped_gemm(const b200moe_gemm_params* p) {
     if ((rc = a.a_merged ? make_map_panels(&ta, p->a, p->M, p->rows, 1, kBM / 64) : make_map_rows(&ta, p->a, p->M, p->rows, 1, 64))) return rc;
     if ((rc = a.b_merged ? make_map_panels(&tb, p->b, p->N, p->rows, 1, kBN / 64) : make_map_rows(&tb, p->b, p->N, p->rows, 1, 64))) return rc;
     if ((rc = make_map_rows(&td, p->d, p->N, p->M, p->num_groups, kHalfM))) return rc;
+    ta_full = ta;
     max_tiles = (long long)p->num_groups * ((p->M + kBM - 1) / kBM) * n_tiles;
   }
   const size_t smem = sizeof(GemmSmem) + 1024;
   if ((rc = set_smem<moe_grouped_gemm_kernel>(smem))) return rc;
-  const long long sms = sm_count(p->device);
+  if (p->max_ctas < 0) return B200ATTN_EINVAL;
+  long long sms = sm_count(p->device);
+  if (p->max_ctas > 0 && p->max_ctas < sms) sms = p->max_ctas;
   const int grid = (int)(max_tiles < sms ? max_tiles : sms);
-  moe_grouped_gemm_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(ta, tb, td, a);
+  moe_grouped_gemm_kernel<<<grid, kGemmThreads, smem, static_cast<cudaStream_t>(p->stream)>>>(ta, ta_full, tb, td, a);
   return launch_status();
 }
 

@@ -142,8 +142,8 @@ struct TileWalker {
 };
 
 __global__ void __launch_bounds__(kGemmThreads, 1)
-moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                        const __grid_constant__ CUtensorMap tm_d, const GemmArgs a) {
+moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_a_full,
+                        const __grid_constant__ CUtensorMap tm_b, const __grid_constant__ CUtensorMap tm_d, const GemmArgs a) {
   extern __shared__ uint8_t smem_raw[];
   GemmSmem* sm = reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -195,6 +195,7 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
     // ------------------------------------ TMA loader ------------------------------------
     if (lane == 0) {
       prefetch_tmap(&tm_a);
+      prefetch_tmap(&tm_a_full);
       prefetch_tmap(&tm_b);
       // As few TMA operations per block as the layouts allow (the engine's issue rate, not its bandwidth, is what a
       // block of seven 8 KB boxes ran into): M/N-contiguous operands whose width is a multiple of 64 are described
@@ -214,8 +215,9 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
           const int a_bytes = (a.a_merged ? 2 : t.halves) * kHalfABytes;   // a merged box always carries both halves
           mbar_arrive_expect_tx(bar, a_bytes + kBBytes);
           if (a.mode == 0) {
-            // A: rows x K, K contiguous: one (64 x 128-row) box per accumulator half
-            for (int h = 0; h < t.halves; ++h) tma_load_4d(sa + h * kHalfABytes, &tm_a, bar, k0, t.row0 + h * kHalfM, 0, 0);
+            // A: rows x K, K contiguous: one box for both accumulator halves
+            if (t.halves == 2) tma_load_4d(sa, &tm_a_full, bar, k0, t.row0, 0, 0);   // (64 x 256-row) box
+            else tma_load_4d(sa, &tm_a, bar, k0, t.row0, 0, 0);                       // half tile: (64 x 128-row) box
             if (!a.b_mn) {
               tma_load_4d(sb, &tm_b, bar, k0, t.n0, t.g, 0);                       // B_g: N x K, K contiguous: one (64 x 192-row) box
             } else if (a.b_merged) {

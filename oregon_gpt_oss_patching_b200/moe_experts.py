@@ -33,7 +33,8 @@ import torch
 from . import _cabi
 from .attention_kernel import _status_word
 
-__all__ = ["moe_experts", "b200_experts_forward", "patch_moe_experts", "unpatch_moe_experts", "route", "padded_rows"]
+__all__ = ["moe_experts", "b200_experts_forward", "patch_moe_experts", "unpatch_moe_experts", "route", "padded_rows",
+           "set_gemm_ctas"]
 
 
 class Routing(NamedTuple):
@@ -57,13 +58,14 @@ def route(router_indices: torch.Tensor, routing_weights: torch.Tensor, num_exper
     align = _cabi.MOE_ROW_ALIGN
     flat = router_indices.reshape(-1).to(torch.int64)
     order = torch.argsort(flat, stable=True)
-    counts = torch.zeros(num_experts, dtype=torch.int64, device=dev).index_add_(
-        0, flat, torch.ones_like(flat))                                   # (bincount would synchronise)
+    sorted_e = flat[order]
+    # first sorted pair of each expert by binary search (bincount would synchronise, index_add_ uses atomics)
+    first = torch.searchsorted(sorted_e, torch.arange(num_experts + 1, device=dev))
+    counts = first[1:] - first[:-1]
+    first = first[:-1]
     padded = (counts + (align - 1)) // align * align
     offsets = torch.zeros(num_experts + 1, dtype=torch.int64, device=dev)
     offsets[1:] = torch.cumsum(padded, 0)
-    first = torch.cumsum(counts, 0) - counts                              # first sorted pair of each expert
-    sorted_e = flat[order]
     dest = offsets[sorted_e] + (torch.arange(T * k, device=dev) - first[sorted_e])
     rows = padded_rows(T * k, num_experts)
     row_token = torch.full((rows,), -1, dtype=torch.int32, device=dev)
@@ -83,13 +85,24 @@ def _stream(dev):
     return ctypes.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
 
 
+# Persistent CTAs of the grouped GEMM (0 = one per SM).  A data-parallel trainer whose gradient all-reduce runs beside
+# the backward pass can leave the collective's SMs free: ``set_gemm_ctas(132)``.
+_gemm_ctas = 0
+
+
+def set_gemm_ctas(n: int) -> None:
+    global _gemm_ctas
+    _gemm_ctas = max(0, int(n))
+
+
 def grouped_gemm(op: int, a, b, d, offsets, *, bias=None, M=0, N=0, K=0) -> None:
     """One ``b200moe_grouped_gemm`` call on the current stream (see include/b200moe.h for the three forms)."""
     dev = a.device
     p = _cabi.MoeGemmParams(op=op, num_groups=offsets.numel() - 1, rows=a.shape[0], M=M, N=N, K=K,
                             offsets=offsets.data_ptr(), a=a.data_ptr(), b=b.data_ptr(),
                             bias=None if bias is None else bias.data_ptr(), d=d.data_ptr(), device=dev.index,
-                            stream=torch.cuda.current_stream(dev).cuda_stream, status=_status_word(dev).data_ptr())
+                            stream=torch.cuda.current_stream(dev).cuda_stream, status=_status_word(dev).data_ptr(),
+                            max_ctas=_gemm_ctas)
     _cabi.check(_cabi.load().b200moe_grouped_gemm(ctypes.byref(p)), "b200moe_grouped_gemm")
 
 

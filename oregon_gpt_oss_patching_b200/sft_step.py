@@ -65,6 +65,8 @@ def main():
                          "can dispatch), or transformers' per-expert loop")
     ap.add_argument("--no-allreduce", action="store_true", help="attribution run: data-parallel replicas that skip the gradient "
                     "all-reduce (the difference to a normal run is the part of the all-reduce that backward does not hide)")
+    ap.add_argument("--gemm-ctas", type=int, default=0, help="persistent CTAs of the grouped GEMM (0 = one per SM); fewer "
+                    "leaves SMs to the all-reduce that runs beside the backward pass")
     ap.add_argument("--hf-rope", action="store_true", help="keep transformers' rotary embedding (default: the one-pass kernel, "
                     "whenever the attention is patched)")
     args = ap.parse_args()
@@ -87,6 +89,7 @@ def main():
     from . import moe_experts
     if args.moe == "b200":
         moe_experts.patch_moe_experts()
+        moe_experts.set_gemm_ctas(args.gemm_ctas)
 
     model, cfg = build_model(args.layers, args.experts, args.vocab, dev, experts_implementation="eager" if args.moe == "hf_eager" else None)
     n_params = sum(p.numel() for p in model.parameters())
@@ -134,7 +137,7 @@ def main():
             "rope": "hf" if (args.unpatched or args.hf_rope) else "b200",
             "moe": args.moe if args.moe != "hf" else "hf:" + str(getattr(cfg, "_experts_implementation", None)), "loss": round(float(loss), 4), "kernel_status": status,
             "config": {"layers": args.layers, "experts": args.experts, "vocab": args.vocab, "seq_len": args.seq,
-                       "params_b": round(n_params / 1e9, 2), "batch_per_gpu": 1, "grad_checkpointing": True,
+                       "params_b": round(n_params / 1e9, 2), "batch_per_gpu": 1, "gemm_ctas": args.gemm_ctas, "grad_checkpointing": True,
                        "optimizer": "sgd (state-free)", "dp": ("replicas, all-reduce skipped (attribution run)" if args.no_allreduce else "replicas + NCCL all-reduce (DDP)") if world > 1 else "none"},
             "peak_mem_gb": round(torch.cuda.max_memory_allocated(dev) / 2**30, 1), "data": "synthetic",
             "wall_s": round(time.perf_counter() - t0, 1)}), flush=True)
