@@ -93,6 +93,27 @@ def test_grouped_gemm_inner_tn(counts, M, N):
     assert last_status(DEV) == 0
 
 
+def test_a_smaller_grid_gives_the_same_bits():
+    """`max_ctas` only changes which persistent CTA computes which tile: results are bit-identical."""
+    from oregon_gpt_oss_patching_b200.moe_experts import set_gemm_ctas
+    counts = [300, 0, 129, 700]
+    off, rows = _segments(counts)
+    offsets = torch.tensor(off, dtype=torch.int32, device=DEV)
+    a, w = _rand(rows, 256, seed=1), _rand(len(counts), 256, 384, scale=1 / 16, seed=2)
+    outs = []
+    for ctas in (0, 5, 1):
+        set_gemm_ctas(ctas)
+        try:
+            d = torch.zeros(rows, 384, dtype=torch.bfloat16, device=DEV)
+            grouped_gemm(_cabi.MOE_ROWS_NN, a, w, d, offsets, N=384, K=256)
+            torch.cuda.synchronize()
+        finally:
+            set_gemm_ctas(0)
+        outs.append(d)
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[2])
+    assert last_status(DEV) == 0
+
+
 def test_memory_bound_kernels_match_tensor_expressions():
     lib = _cabi.load()
     st = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
