@@ -200,8 +200,9 @@ int b200moe_bias_grad(const void* dy, const int32_t* offsets, void* db, int32_t 
   if ((rc = check_matrix(dy, cols)) || (rc = check_matrix(db, cols)) || (rc = check_device(device))) return rc;
   DeviceGuard guard(device);
   if (!guard.ok) return B200ATTN_ECUDA;
-  const dim3 grid((cols + 255) / 256, num_groups);
-  moe_bias_grad_kernel<<<grid, kBiasGradWarps * 32, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(dy), offsets,
+  const int cols_per_block = kBiasGradColLanes * 8;
+  const dim3 grid((cols + cols_per_block - 1) / cols_per_block, num_groups);
+  moe_bias_grad_kernel<<<grid, kBiasGradRowLanes * kBiasGradColLanes, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const __nv_bfloat16*>(dy), offsets,
                                                                              static_cast<__nv_bfloat16*>(db), cols);
   return launch_status();
 }

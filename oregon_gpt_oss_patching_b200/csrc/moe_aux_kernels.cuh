@@ -147,38 +147,40 @@ __global__ void moe_glu_bwd_kernel(const __nv_bfloat16* __restrict__ y1, const _
 }
 
 // db[g, c] = sum over the rows r of group g of dy[r, c], in fp32, in an order fixed by the launch shape alone.
-// Block = (group, 256 columns), 8 warps: warp w sums rows r0 + w, r0 + w + 8, ... (a lane owns 8 columns: one
-// 16-byte load per row, 512 contiguous bytes per warp), then the eight partials are added in warp order.
-constexpr int kBiasGradWarps = 8;
-__global__ void __launch_bounds__(kBiasGradWarps * 32)
+// Block = (group, 128 columns), 256 threads as 16 column lanes x 16 row lanes: a thread owns 8 columns (one 16-byte
+// load per row) and sums rows r0 + y, r0 + y + 16, ...; the sixteen partials of a column are then added in row-lane
+// order.  (128 columns per block rather than 256: twice the blocks and loads in flight for the 2880-column case.)
+constexpr int kBiasGradRowLanes = 16;
+constexpr int kBiasGradColLanes = 16;
+__global__ void __launch_bounds__(kBiasGradRowLanes * kBiasGradColLanes)
 moe_bias_grad_kernel(const __nv_bfloat16* __restrict__ dy, const int* __restrict__ offsets,
                      __nv_bfloat16* __restrict__ db, int cols) {
-  __shared__ float part[kBiasGradWarps][32][9];   // (padded: lanes of a warp hit different banks)
+  __shared__ float part[kBiasGradRowLanes][kBiasGradColLanes][9];   // (padded against bank conflicts)
   const int g = blockIdx.y;
-  const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
-  const int c0 = (blockIdx.x * 32 + lane) * 8;
+  const int x = threadIdx.x % kBiasGradColLanes, y = threadIdx.x / kBiasGradColLanes;
+  const int c0 = (blockIdx.x * kBiasGradColLanes + x) * 8;
   const int r0 = offsets[g], r1 = offsets[g + 1];
   float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
   if (c0 < cols) {
     const uint4* col = reinterpret_cast<const uint4*>(dy + c0);
     const long long stride = cols >> 3;
 #pragma unroll 4
-    for (int r = r0 + w; r < r1; r += kBiasGradWarps) {
+    for (int r = r0 + y; r < r1; r += kBiasGradRowLanes) {
       const uint4 v = __ldg(col + r * stride);
       acc[0] += bf16_lo(v.x); acc[1] += bf16_hi(v.x); acc[2] += bf16_lo(v.y); acc[3] += bf16_hi(v.y);
       acc[4] += bf16_lo(v.z); acc[5] += bf16_hi(v.z); acc[6] += bf16_lo(v.w); acc[7] += bf16_hi(v.w);
     }
   }
 #pragma unroll
-  for (int e = 0; e < 8; ++e) part[w][lane][e] = acc[e];
+  for (int e = 0; e < 8; ++e) part[y][x][e] = acc[e];
   __syncthreads();
-  if (w == 0 && c0 < cols) {
+  if (y == 0 && c0 < cols) {
     float s[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-      s[e] = part[0][lane][e];
+      s[e] = part[0][x][e];
 #pragma unroll
-      for (int k = 1; k < kBiasGradWarps; ++k) s[e] += part[k][lane][e];
+      for (int k = 1; k < kBiasGradRowLanes; ++k) s[e] += part[k][x][e];
     }
     *reinterpret_cast<uint4*>(db + (long long)g * cols + c0) =
         make_uint4(pack2(s[0], s[1]), pack2(s[2], s[3]), pack2(s[4], s[5]), pack2(s[6], s[7]));
