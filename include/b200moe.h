@@ -51,6 +51,8 @@ typedef struct b200moe_gemm_params {
   int32_t device;
   void* stream;           /* cudaStream_t */
   int32_t* status;        /* device int32, may be NULL */
+  void* glu_out;          /* ROWS_NN only, or NULL: (rows x N/2) bf16 that receives b200moe_glu of D's rows from the
+                             same launch (N a multiple of 16), so that the activation needs no pass of its own */
   int32_t max_ctas;       /* 0: one persistent CTA per SM.  > 0: at most this many, for callers that run another
                              kernel beside it (a collective's CTAs hold SMs, and a persistent CTA without an SM
                              waits for one to finish all of its tiles) */

@@ -57,7 +57,7 @@ class MoeGemmParams(ctypes.Structure):
         ("M", ctypes.c_int32), ("N", ctypes.c_int32), ("K", ctypes.c_int32),
         ("offsets", ctypes.c_void_p), ("a", ctypes.c_void_p), ("b", ctypes.c_void_p), ("bias", ctypes.c_void_p),
         ("d", ctypes.c_void_p), ("device", ctypes.c_int32), ("stream", ctypes.c_void_p), ("status", ctypes.c_void_p),
-        ("max_ctas", ctypes.c_int32),
+        ("glu_out", ctypes.c_void_p), ("max_ctas", ctypes.c_int32),
     ]
 
 

@@ -6,8 +6,7 @@
 #include <cuda_runtime.h>
 
 #include "host_common.cuh"
-#include "moe_aux_kernels.cuh"
-#include "moe_gemm_kernel.cuh"
+#include "moe_gemm_kernel.cuh"   // (includes moe_aux_kernels.cuh)
 
 namespace {
 
@@ -73,6 +72,7 @@ int b200moe_grouped_gemm(const b200moe_gemm_params* p) {
   if (p->N % 8 != 0 || (inner ? p->M % 8 != 0 : p->K % 8 != 0)) return B200ATTN_EALIGN;
   if (!aligned16(p->a) || !aligned16(p->b) || !aligned16(p->d) || (p->bias != nullptr && !aligned16(p->bias))) return B200ATTN_EALIGN;
   if (inner && p->bias != nullptr) return B200ATTN_EINVAL;
+  if (p->glu_out != nullptr && (p->op != B200MOE_ROWS_NN || p->N % 16 != 0 || !aligned16(p->glu_out))) return B200ATTN_EINVAL;
   int rc = check_device(p->device);
   if (rc) return rc;
   DeviceGuard guard(p->device);
@@ -86,6 +86,7 @@ int b200moe_grouped_gemm(const b200moe_gemm_params* p) {
   a.K = inner ? 0 : p->K;
   a.offsets = p->offsets;
   a.bias = static_cast<const __nv_bfloat16*>(p->bias);
+  a.glu_out = static_cast<__nv_bfloat16*>(p->glu_out);
   a.status = p->status;
   CUtensorMap ta, ta_full, tb, td;
   long long max_tiles;

@@ -27,10 +27,13 @@
 // panels).  Warp 1 lane 0: every MMA (warp 1 owns the tensor memory).  Warps 4-7 / 8-11: epilogue of
 // accumulator rows 0-127 / 128-255 in two phases: tensor memory -> (+ bias) -> packed bf16 in registers, which
 // releases the accumulators to the next tile's MMAs; then registers -> shared memory (swizzled 128 x 64 tile) ->
-// one TMA store per 64 columns; rows or columns past the end of D are clipped by the store.  Every wait is bounded.
+// one TMA store per 64 columns; rows or columns past the end of D are clipped by the store.  The first GEMM of the
+// block also writes the gated activation of its (gate, up) column pairs from the same registers (`glu_out`), so that
+// H needs no pass of its own.  Every wait is bounded.
 #pragma once
 #include <cuda.h>
 
+#include "moe_aux_kernels.cuh"
 #include "sm100_ptx.cuh"
 
 namespace b200moe {
@@ -73,6 +76,7 @@ struct GemmArgs {
   int M, N, K;        // mode 0: N output columns, K inner (M unused: rows come from offsets); mode 1: M x N per group (K unused)
   const int* offsets; // (num_groups + 1) row offsets of the groups, multiples of 128
   const __nv_bfloat16* bias;   // (num_groups, N) or nullptr
+  __nv_bfloat16* glu_out;      // mode 0 only, or nullptr: (rows x N/2), the gated activation of D's (gate, up) column pairs
   int* status;
 };
 
@@ -363,6 +367,23 @@ moe_grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_c
 #pragma unroll
       for (int c = 0; c < kBN / 64; ++c) {
         if (c < n_chunks) {
+          if (a.glu_out != nullptr) {
+            // the gated activation of this row's 32 (gate, up) pairs, from the bf16 values D holds: 64 bytes per row,
+            // written straight from registers (under the next tile's MMAs)
+            const int pairs_valid = (a.N - (t.n0 + c * 64)) >> 1;
+            __nv_bfloat16* dst = a.glu_out + (long long)(t.row0 + wg * kHalfM + r) * (a.N >> 1) + ((t.n0 + c * 64) >> 1);
+            if (pairs_valid >= 32) {
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                reinterpret_cast<uint4*>(dst)[q] =
+                    make_uint4(pack2(glu_value(pk[c][q * 8]), glu_value(pk[c][q * 8 + 1])), pack2(glu_value(pk[c][q * 8 + 2]), glu_value(pk[c][q * 8 + 3])),
+                               pack2(glu_value(pk[c][q * 8 + 4]), glu_value(pk[c][q * 8 + 5])), pack2(glu_value(pk[c][q * 8 + 6]), glu_value(pk[c][q * 8 + 7])));
+            } else {
+#pragma unroll
+              for (int e = 0; e < 32; ++e)
+                if (e < pairs_valid) dst[e] = __float2bfloat16_rn(glu_value(pk[c][e]));
+            }
+          }
           // the previous store of this warpgroup must have read the staging tile
           if (leader) tma_store_wait_read();
           if (wg_barrier_or(1 + wg, failed)) { failed = true; break; }

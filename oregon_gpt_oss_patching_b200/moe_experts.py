@@ -8,7 +8,7 @@ Once attention is fast this loop is the largest part of a fine-tuning step.  Her
 as grouped GEMMs on the tensor cores over token rows sorted by expert, behind the C ABI of
 ``include/b200moe.h``:
 
-    forward    rows sorted by expert -> X_s;  Y1 = X_s W1_e + b1_e;  H = glu(Y1);  Y2 = H W2_e + b2_e;
+    forward    rows sorted by expert -> X_s;  Y1 = X_s W1_e + b1_e and H = glu(Y1) from one launch;  Y2 = H W2_e + b2_e;
                out[t] = sum_j w[t, j] * Y2[row of (t, j)]
     backward   dW2_e = H_e^T dY2_e, dH = dY2 W2_e^T, dY1 = glu'(Y1) dH, dW1_e = X_e^T dY1_e, dX_s = dY1 W1_e^T,
                bias gradients as per-expert column sums, d w[t, j] = <d out[t], Y2[row of (t, j)]>
@@ -95,14 +95,14 @@ def set_gemm_ctas(n: int) -> None:
     _gemm_ctas = max(0, int(n))
 
 
-def grouped_gemm(op: int, a, b, d, offsets, *, bias=None, M=0, N=0, K=0) -> None:
+def grouped_gemm(op: int, a, b, d, offsets, *, bias=None, glu_out=None, M=0, N=0, K=0) -> None:
     """One ``b200moe_grouped_gemm`` call on the current stream (see include/b200moe.h for the three forms)."""
     dev = a.device
     p = _cabi.MoeGemmParams(op=op, num_groups=offsets.numel() - 1, rows=a.shape[0], M=M, N=N, K=K,
                             offsets=offsets.data_ptr(), a=a.data_ptr(), b=b.data_ptr(),
                             bias=None if bias is None else bias.data_ptr(), d=d.data_ptr(), device=dev.index,
                             stream=torch.cuda.current_stream(dev).cuda_stream, status=_status_word(dev).data_ptr(),
-                            max_ctas=_gemm_ctas)
+                            glu_out=None if glu_out is None else glu_out.data_ptr(), max_ctas=_gemm_ctas)
     _cabi.check(_cabi.load().b200moe_grouped_gemm(ctypes.byref(p)), "b200moe_grouped_gemm")
 
 
@@ -142,9 +142,12 @@ class _moe_experts(torch.autograd.Function):
         xs = torch.empty(rows, H, **bf)
         _cabi.check(lib.b200moe_gather_rows(_ptr(hidden), _ptr(r.row_token), None, _ptr(xs), rows, H, di, st), "b200moe_gather_rows")
         y1 = torch.empty(rows, I2, **bf)
-        grouped_gemm(_cabi.MOE_ROWS_NN, xs, w1, y1, r.offsets, bias=b1, N=I2, K=H)
         h = torch.empty(rows, I, **bf)
-        _cabi.check(lib.b200moe_glu(_ptr(y1), _ptr(h), rows, I, di, st), "b200moe_glu")
+        if I2 % 16 == 0:   # the gated activation leaves the first GEMM's epilogue (rows past the last expert stay unwritten, and unread)
+            grouped_gemm(_cabi.MOE_ROWS_NN, xs, w1, y1, r.offsets, bias=b1, glu_out=h, N=I2, K=H)
+        else:
+            grouped_gemm(_cabi.MOE_ROWS_NN, xs, w1, y1, r.offsets, bias=b1, N=I2, K=H)
+            _cabi.check(lib.b200moe_glu(_ptr(y1), _ptr(h), rows, I, di, st), "b200moe_glu")
         y2 = torch.empty(rows, H, **bf)
         grouped_gemm(_cabi.MOE_ROWS_NN, h, w2, y2, r.offsets, bias=b2, N=H, K=I)
         weights = routing_weights.to(torch.float32).contiguous()

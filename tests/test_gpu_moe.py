@@ -52,7 +52,8 @@ def test_grouped_gemm_rows_nn_and_nt(counts, K, N):
     bias = _rand(E, N, seed=3)
     sentinel = 777.0
     d = torch.full((rows, N), sentinel, dtype=torch.bfloat16, device=DEV)
-    grouped_gemm(_cabi.MOE_ROWS_NN, a, w_nn, d, offsets, bias=bias, N=N, K=K)
+    h = torch.full((rows, N // 2), sentinel, dtype=torch.bfloat16, device=DEV) if N % 16 == 0 else None
+    grouped_gemm(_cabi.MOE_ROWS_NN, a, w_nn, d, offsets, bias=bias, glu_out=h, N=N, K=K)
     d_t = torch.full((rows, N), sentinel, dtype=torch.bfloat16, device=DEV)
     w_nt = w_nn.transpose(1, 2).contiguous()          # (E, N, K): the same products from the transposed storage
     grouped_gemm(_cabi.MOE_ROWS_NT, a, w_nt, d_t, offsets, N=N, K=K)
@@ -64,6 +65,13 @@ def test_grouped_gemm_rows_nn_and_nt(counts, K, N):
         ref = a[seg].float() @ w_nn[e].float()
         assert rel(d[seg], ref + bias[e].float()) < TOL, ("nn", e)
         assert rel(d_t[seg], ref) < TOL, ("nt", e)
+    if h is not None:
+        # the gated activation from the same launch is, bit for bit, the separate kernel applied to the rows of D
+        h_sep = torch.empty_like(h)
+        _cabi.check(_cabi.load().b200moe_glu(ctypes.c_void_p(d.data_ptr()), ctypes.c_void_p(h_sep.data_ptr()), rows, N // 2, 0,
+                                             ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)), "glu")
+        torch.cuda.synchronize()
+        assert torch.equal(h[:off[-1]], h_sep[:off[-1]]) and bool((h[off[-1]:] == sentinel).all())
     # rows that belong to no group are not written
     assert bool((d[off[-1]:] == sentinel).all()) and bool((d_t[off[-1]:] == sentinel).all())
     assert last_status(DEV) == 0
