@@ -11,7 +11,8 @@ rank runs the same per-GPU workload on its own (batch x KV-group) units -- atten
 exchange between units, so there is no collective on the data path; only the timing is
 reduced (max over ranks).  One JSON line is printed by rank 0.
 
-At N = 1 the line also carries `triton_reference`: the reference project's own Triton kernel run
+At N = 1 the line also carries `moe_block` (the expert block that follows attention in every layer: this library's
+grouped-GEMM path next to transformers' own, see bench_moe.py) and `triton_reference`: the reference project's own Triton kernel run
 through its stock `attention()` on the same GPU, same seeded inputs and same event protocol
 (imported from `--reference-path`, `$REFERENCE_PATH` or `baseline/_ref`; "unavailable" with the
 reason when it cannot be imported), and `cpu_baseline_cfg1`: the unmodified `transformers`
@@ -399,6 +400,14 @@ def run_b200(args, rank, world, local_rank):
         line["strong"] = strong
     if world == 1 and not args.no_contender:
         line["triton_reference"] = triton_contender(args, case, (qd, kd, vd, dod, sinks), seqlens, stream)
+    if world == 1 and not args.no_contender and not args.shape:
+        # the block that follows attention in every layer, measured in the same process (a record, not the headline)
+        torch.cuda.empty_cache()
+        try:
+            from bench_moe import summary_record
+            line["moe_block"] = summary_record(local_rank)
+        except Exception as exc:   # noqa: BLE001
+            line["moe_block"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_sample(args.workload, budget_s=args.cpu_budget)
         line["cpu_baseline_cfg1"] = cpu_hf_eager_cfg1()

@@ -230,6 +230,44 @@ def run_moe(args, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def summary_record(device_index: int, tokens: int = 8192, steps: int = 10) -> dict:
+    """A compact record of the expert block for the attention benchmark's N = 1 line: this library's forward + backward
+    and transformers' default implementation (`torch._grouped_mm`) on the same weights and inputs."""
+    from oregon_gpt_oss_patching_b200 import moe_experts as me
+    dev = torch.device("cuda", device_index)
+    stream = torch.cuda.current_stream(dev)
+    hidden, idx, weights, w1, b1, w2, b2, dout = _inputs(tokens, dev)
+    flops = block_flops(tokens * TOPK)
+    leaves = [t.requires_grad_(True) for t in (hidden, weights, w1, b1, w2, b2)]
+
+    def step():
+        for t in leaves:
+            t.grad = None
+        me.moe_experts(leaves[0], idx, *leaves[1:]).backward(dout)
+
+    ms = _time(step, steps, 3, stream)
+    rec = {"workload": f"one gpt-oss-20b expert block, {tokens} tokens, top-{TOPK} of {E}, fwd+bwd (`bench.py --workload moe` has the full line)",
+           "ms_per_step": round(ms, 4), "tflops": round(flops / (ms * 1e-3) / 1e12, 1)}
+    for t in leaves:
+        t.grad = None
+    try:
+        mod = _hf_module((w1.detach(), b1.detach(), w2.detach(), b2.detach()), "grouped_mm", dev, torch.bfloat16)
+        h_in, w_in = hidden.detach().clone().requires_grad_(True), weights.detach().clone().requires_grad_(True)
+
+        def hf_step():
+            for p_ in mod.parameters():
+                p_.grad = None
+            h_in.grad = None
+            w_in.grad = None
+            mod(h_in, idx, w_in).backward(dout)
+
+        hf_ms = _time(hf_step, max(3, steps // 3), 2, stream)
+        rec["hf_grouped_mm"] = {"ms_per_step": round(hf_ms, 3), "vs_b200": round(hf_ms / ms, 3)}
+    except Exception as exc:   # noqa: BLE001
+        rec["hf_grouped_mm"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:120]}"}
+    return rec
+
+
 def cpu_sample(tokens: int = 256) -> dict:
     """Hugging Face's per-expert loop (fp32) on the host cores: forward + backward of the same block on `tokens` tokens."""
     torch.set_num_threads(max(1, torch.get_num_threads()))
