@@ -101,6 +101,57 @@ def test_grouped_gemm_inner_tn(counts, M, N):
     assert last_status(DEV) == 0
 
 
+def _banded(shape, band=4096):
+    """A tensor of `shape` carved out of the middle of a larger allocation filled with a sentinel; returns (view, whole)."""
+    n = 1
+    for x in shape:
+        n *= x
+    whole = torch.full((n + 2 * band,), 777.0, dtype=torch.bfloat16, device=DEV)
+    return whole[band:band + n].view(shape), whole
+
+
+def _bands_untouched(whole, shape, band=4096):
+    n = 1
+    for x in shape:
+        n *= x
+    return bool((whole[:band] == 777.0).all()) and bool((whole[band + n:] == 777.0).all())
+
+
+@pytest.mark.parametrize("K,N,M", [(72, 200, 200), (64, 192, 256), (2880, 384, 320)])
+def test_nothing_is_written_outside_the_output_buffers(K, N, M):
+    """Every output sits inside a larger sentinel-filled allocation (the stand-in for a memory checker): ragged
+    widths and row counts (clipped TMA stores, half tiles, an empty group) must leave the bands as they were."""
+    lib, st = _cabi.load(), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    counts = [129, 0, 1, 300]
+    off, rows = _segments(counts)
+    E = len(counts)
+    offsets = torch.tensor(off, dtype=torch.int32, device=DEV)
+    a = _rand(rows, K, seed=1)
+    d, d_whole = _banded((rows, N))
+    grouped_gemm(_cabi.MOE_ROWS_NN, a, _rand(E, K, N, scale=K ** -0.5, seed=2), d, offsets, bias=_rand(E, N, seed=3), N=N, K=K)
+    dt, dt_whole = _banded((rows, N))
+    grouped_gemm(_cabi.MOE_ROWS_NT, a, _rand(E, N, K, scale=K ** -0.5, seed=4), dt, offsets, N=N, K=K)
+    dw, dw_whole = _banded((E, M, N))
+    grouped_gemm(_cabi.MOE_INNER_TN, _rand(rows, M, seed=5), _rand(rows, N, seed=6), dw, offsets, M=M, N=N)
+    db, db_whole = _banded((E, N))
+    _cabi.check(lib.b200moe_bias_grad(ctypes.c_void_p(d.data_ptr()), ctypes.c_void_p(offsets.data_ptr()), ctypes.c_void_p(db.data_ptr()),
+                                      E, N, 0, st), "bias_grad")
+    row_src = torch.full((rows,), -1, dtype=torch.int32, device=DEV)
+    row_src[:100] = torch.arange(100, dtype=torch.int32, device=DEV)
+    g_out, g_whole = _banded((rows, N))
+    _cabi.check(lib.b200moe_gather_rows(ctypes.c_void_p(d.data_ptr()), ctypes.c_void_p(row_src.data_ptr()), None,
+                                        ctypes.c_void_p(g_out.data_ptr()), rows, N, 0, st), "gather")
+    pos = torch.randint(0, rows, (50, 3), dtype=torch.int32, device=DEV)
+    c_out, c_whole = _banded((50, N))
+    _cabi.check(lib.b200moe_combine_rows(ctypes.c_void_p(dt.data_ptr()), ctypes.c_void_p(pos.data_ptr()), None,
+                                         ctypes.c_void_p(c_out.data_ptr()), 50, 3, N, 0, st), "combine")
+    torch.cuda.synchronize()
+    for whole, shape in ((d_whole, (rows, N)), (dt_whole, (rows, N)), (dw_whole, (E, M, N)), (db_whole, (E, N)),
+                         (g_whole, (rows, N)), (c_whole, (50, N))):
+        assert _bands_untouched(whole, shape), shape
+    assert last_status(DEV) == 0
+
+
 def test_a_smaller_grid_gives_the_same_bits():
     """`max_ctas` only changes which persistent CTA computes which tile: results are bit-identical."""
     from oregon_gpt_oss_patching_b200.moe_experts import set_gemm_ctas
