@@ -401,6 +401,20 @@ def run_b200(args, rank, world, local_rank):
     if world == 1 and not args.no_contender:
         line["triton_reference"] = triton_contender(args, case, (qd, kd, vd, dod, sinks), seqlens, stream)
     if world == 1 and not args.no_contender and not args.shape:
+        # the rotary pass in front of attention: one kernel per tensor, read + write once, against the HBM peak
+        try:
+            from oregon_gpt_oss_patching_b200.rope import rope
+            ang = torch.arange(S, device=dev, dtype=torch.float32)[:, None] / (150000.0 ** (torch.arange(0, d, 2, device=dev) / d))[None, :]
+            cos, sin = ang.cos()[None].to(torch.bfloat16), ang.sin()[None].to(torch.bfloat16)
+            q_view = qd.transpose(1, 2).contiguous().transpose(1, 2)     # (B,S,H,d) memory, as the projection leaves it
+            ms_rope = time_steps(lambda: rope(q_view, cos, sin), 20, stream)
+            nbytes = 2 * q_view.numel() * 2
+            line["rope"] = {"ms": round(ms_rope, 4), "gbs": round(nbytes / (ms_rope * 1e-3) / 1e9, 1),
+                            "frac_of_hbm_peak": round(nbytes / (ms_rope * 1e-3) / 1e9 / peaks["hbm_gbs"], 3),
+                            "what": f"b200attn_rope on q of this workload ({q_view.numel() * 2 >> 20} MiB, (B,S,H,d) memory viewed (B,H,S,d))"}
+            del q_view
+        except Exception as exc:   # noqa: BLE001
+            line["rope"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:160]}"}
         # the block that follows attention in every layer, measured in the same process (a record, not the headline)
         torch.cuda.empty_cache()
         try:
