@@ -28,7 +28,7 @@
 
 namespace b200attn {
 
-constexpr int kDkvStages = 3;
+constexpr int kDkvStages = 4;
 constexpr int kDkvThreads = 384;
 constexpr int kDkvTmemCols = 512;
 // tensor-memory columns: S^T [0,128)  dP^T [128,256)  P^T bf16 [256,320)  dS^T bf16 [320,384)  dV [384,448)  dK [448,512)

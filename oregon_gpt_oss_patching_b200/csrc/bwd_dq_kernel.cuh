@@ -31,7 +31,7 @@
 
 namespace b200attn {
 
-constexpr int kDqStages = 3;
+constexpr int kDqStages = 4;
 constexpr int kDqThreads = 384;
 constexpr int kDqTmemCols = 512;
 // tensor-memory columns: S [0,128)  dP [128,256)  dS bf16 [256,320) and [448,512) (two buffers)  Q bf16 [320,352)

@@ -31,7 +31,7 @@
 
 namespace b200attn {
 
-constexpr int kFwdStages = 3;
+constexpr int kFwdStages = 4;
 constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax A, softmax B, {MMA warp A, TMA warp, MMA warp B, idle warp}
 constexpr int kFwdTmemCols = 512;
 // tensor-memory columns: S_A [0,128) S_B [128,256) P_A [256,320) P_B [320,384) O_A [384,448) O_B [448,512)
