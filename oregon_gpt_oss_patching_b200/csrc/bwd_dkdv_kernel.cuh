@@ -16,7 +16,7 @@
 // and is accumulated in fp32 (the reference adds bf16 partial tiles into global memory with
 // atomics, attention_kernel.py:201-212).
 //
-// Pipeline.  Warp 9 streams Q/dO tiles (+ the side tile) through a 3-stage TMA ring.
+// Pipeline.  Warp 9 streams Q/dO tiles (+ the side tile) through a 4-stage TMA ring.
 // Warp 8 issues the S^T/dP^T MMAs and warp 10 the dV/dK MMAs.  The two compute warpgroups split
 // the 128 query columns of an item (warps 0-3: columns 0-63, warps 4-7: columns 64-127), pull
 // their half of S^T/dP^T into registers and release those columns at once, so the tensor core

@@ -20,7 +20,7 @@
 //
 // Q and dO (the A operands of S and dP for the CTA's whole life) are copied once into tensor
 // memory as bf16, so those MMAs read only the K/V tile from shared memory.  Pipeline as in the
-// dK/dV kernel: warp 9 streams K/V tiles through a 3-stage TMA ring, warp 8 issues the S/dP MMAs
+// dK/dV kernel: warp 9 streams K/V tiles through a 4-stage TMA ring, warp 8 issues the S/dP MMAs
 // and warp 10 the dQ MMAs, the two compute warpgroups split the 128 key columns of an
 // item, pull their half of S/dP into registers and release those columns at once (the tensor
 // core computes the next item's S/dP under this item's exponentials), and write dS to its own
