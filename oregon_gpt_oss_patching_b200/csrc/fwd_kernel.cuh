@@ -189,7 +189,7 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       uint32_t pk[16];
-      if (c == 2 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);
+      if (c == 1 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);
       if (kMask && kClassify && kind[c] == kChunkNone) {
 #pragma unroll
         for (int k = 0; k < 16; ++k) pk[k] = 0u;
@@ -211,7 +211,8 @@ __device__ __forceinline__ bool fwd_softmax_tile(FwdRowState& st, int t, uint32_
 #pragma unroll
     for (int c = 0; c < 4; ++c) {
       if (c < 3) tmem_ld32(tmem_s_row + (c + 1) * 32, s[c + 1]);   // in flight under this chunk's exponentials
-      if (c == 2 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);   // hand over early: covers the wake-up latency
+      if (c == 1 && bar_exp_other != 0u) mbar_arrive(bar_exp_other);   // hand over after the first chunk: the other tile wakes, loads and
+                                                                         // classifies under this tile's remaining three (measured against 0, 2 and 3)
       int kind = kChunkAll;
       if (kMask) {
         const uint32_t bits = visible_keys32(i, kv0 + c * 32, window, len);
