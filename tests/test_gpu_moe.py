@@ -12,7 +12,7 @@ from conftest import GOLDEN_DIR
 from oracle.moe_fp32 import MOE_CASES, MoeCase, apply_gate, make_moe_inputs, moe_experts_fwd_bwd
 from oregon_gpt_oss_patching_b200 import _cabi
 from oregon_gpt_oss_patching_b200.attention_kernel import last_status
-from oregon_gpt_oss_patching_b200.moe_experts import (b200_experts_forward, grouped_gemm, moe_experts, patch_moe_experts,
+from oregon_gpt_oss_patching_b200.moe_experts import (grouped_gemm, moe_experts, patch_moe_experts,
                                                       route, unpatch_moe_experts)
 
 pytestmark = pytest.mark.gpu
