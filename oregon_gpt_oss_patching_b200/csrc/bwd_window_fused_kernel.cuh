@@ -169,12 +169,46 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
                  bar_dq_free = smem_u32(&sm->bar_dq_free);
   volatile int* abort_flag = &sm->abort_flag;
 
-  if (tid == 0) {
+  // The loading thread sets up the barriers of its own copies and starts them at once: K, V and the first items'
+  // tiles are on their way while the rest of the CTA is still being set up (tensor-memory allocation, constant
+  // tiles).  It also owns the walk over the items: a head's query tiles, then the next head of the group.
+  int ld_h = g * a.group, ld_qi = 0, ld_it = 0;
+  auto issue_load = [&](int it) -> bool {
+    const int s = it % kFwStages;
+    if (it >= kFwStages && !mbar_wait(smem_u32(&sm->bar_in_empty[s]), ((it / kFwStages) - 1) & 1, abort_flag)) return false;
+    const int item_q0 = (qt_first + ld_qi) * kTile;
+    const uint32_t bar = smem_u32(&sm->bar_in_full[s]);
+    const long long row_off = ((long long)(b * a.Hq + ld_h)) * a.S_pad + item_q0;
+    mbar_arrive_expect_tx(bar, kFwStageBytes);
+    tma_load_4d(smem_u32(sm->q[s]), &tm_q, bar, 0, item_q0, ld_h, b);
+    tma_load_4d(smem_u32(sm->d_o[s]), &tm_do, bar, 0, item_q0, ld_h, b);
+    bulk_load_1d(smem_u32(sm->side[s]), side_base + row_off * kSideRowBytes, kSideTileBytes, bar);
+    bulk_load_1d(smem_u32(sm->w[s]), w_base + row_off, kTile * 4, bar);
+    *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
+    if (++ld_qi == nq) {
+      ld_qi = 0;
+      ++ld_h;
+    }
+    return true;
+  };
+  if (tid == 9 * 32) {
     mbar_init(bar_kv, 1);
     for (int s = 0; s < kFwStages; ++s) {
       mbar_init(smem_u32(&sm->bar_in_full[s]), 1);
       mbar_init(smem_u32(&sm->bar_in_empty[s]), 1);
     }
+    sm->loads_issued = 0;
+    fence_mbar_init();
+    prefetch_tmap(&tm_q);
+    prefetch_tmap(&tm_k);
+    prefetch_tmap(&tm_v);
+    prefetch_tmap(&tm_do);
+    mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
+    tma_load_4d(smem_u32(sm->k), &tm_k, bar_kv, 0, kv0, g, b);
+    tma_load_4d(smem_u32(sm->v), &tm_v, bar_kv, 0, kv0, g, b);
+    for (; ld_it < min(kFwStages, n_items); ++ld_it) issue_load(ld_it);   // (the first ring-full waits for nothing)
+  }
+  if (tid == 0) {
     mbar_init(bar_s_full, 1);
     mbar_init(bar_s_free, 2 * kComputeThreads);
     mbar_init(bar_p_full, 2 * kComputeThreads);
@@ -183,7 +217,6 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
     mbar_init(bar_dq_free, kComputeThreads);
     mbar_init(bar_acc, 1);
     sm->abort_flag = 0;
-    sm->loads_issued = 0;
     fence_mbar_init();
   }
   if (tid < kTile) {
@@ -212,35 +245,9 @@ attn_bwd_window_fused_kernel(const __grid_constant__ CUtensorMap tm_q, const __g
     asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
     if (warp == 9) {
       // ------------------------------------ TMA loader ------------------------------------
-      if (lane == 0) {
-        prefetch_tmap(&tm_q);
-        prefetch_tmap(&tm_k);
-        prefetch_tmap(&tm_v);
-        prefetch_tmap(&tm_do);
-        mbar_arrive_expect_tx(bar_kv, 2 * kTileBytes);
-        tma_load_4d(smem_u32(sm->k), &tm_k, bar_kv, 0, kv0, g, b);
-        tma_load_4d(smem_u32(sm->v), &tm_v, bar_kv, 0, kv0, g, b);
-        int h = g * a.group, qi = 0;   // items run over a head's query tiles, then the next head of the group
-        auto issue_load = [&](int it) -> bool {
-          const int s = it % kFwStages;
-          if (it >= kFwStages && !mbar_wait(smem_u32(&sm->bar_in_empty[s]), ((it / kFwStages) - 1) & 1, abort_flag)) return false;
-          const int item_q0 = (qt_first + qi) * kTile;
-          const uint32_t bar = smem_u32(&sm->bar_in_full[s]);
-          const long long row_off = ((long long)(b * a.Hq + h)) * a.S_pad + item_q0;
-          mbar_arrive_expect_tx(bar, kFwStageBytes);
-          tma_load_4d(smem_u32(sm->q[s]), &tm_q, bar, 0, item_q0, h, b);
-          tma_load_4d(smem_u32(sm->d_o[s]), &tm_do, bar, 0, item_q0, h, b);
-          bulk_load_1d(smem_u32(sm->side[s]), side_base + row_off * kSideRowBytes, kSideTileBytes, bar);
-          bulk_load_1d(smem_u32(sm->w[s]), w_base + row_off, kTile * 4, bar);
-          *reinterpret_cast<volatile int*>(&sm->loads_issued) = it + 1;
-          if (++qi == nq) {
-            qi = 0;
-            ++h;
-          }
-          return true;
-        };
+      if (lane == 0) {   // (K, V and the first items were requested before the CTA-wide barrier)
         bool ok = true;
-        for (int it = 0; ok && it < n_items; ++it) ok = issue_load(it);
+        for (int it = ld_it; ok && it < n_items; ++it) ok = issue_load(it);
         if (!ok) report_abort(a);
       }
       __syncwarp();
