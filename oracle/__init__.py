@@ -24,6 +24,14 @@ unmodified ``transformers`` eager function in fp32 and (2) the reference's
 Triton kernels under the Triton CPU interpreter (fp32), and stores their
 outputs as fixtures in ``tests/golden``.  ``tests/test_oracle.py`` checks
 every oracle implementation here against those fixtures.
+
+The steps either side of attention
+----------------------------------
+``moe_fp32`` restates the expert block (``modeling_gpt_oss.py:76-114``) and is pinned by
+``tests/golden/moe_*.npz`` (made by ``tests/golden/make_golden_moe.py`` from the unmodified module);
+``rope_fp32`` restates the rotary embedding (``modeling_gpt_oss.py:226-242``) and is pinned against
+the installed function itself in ``tests/test_rope_oracle.py``.  Both are imported by name
+(``oracle.moe_fp32``, ``oracle.rope_fp32``), by the tests and the smoke check only.
 """
 from .eager_fp32 import (  # noqa: F401
     AttnCase,
