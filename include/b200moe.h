@@ -74,6 +74,23 @@ size_t b200moe_sizeof_gemm_params(void);
 int b200moe_grouped_gemm(const b200moe_gemm_params* p);
 
 /*
+ * Routing bookkeeping, one launch: sorts the tokens * top_k (token, choice) pairs by expert (stable: pairs of one
+ * expert keep their order) into segments that start at multiples of B200MOE_ROW_ALIGN rows.  Replaces the
+ * `one_hot` / `nonzero` / `torch.where` bookkeeping of GptOssExperts.forward (modeling_gpt_oss.py:86-103), which
+ * synchronises with the host once per expert; nothing here does.
+ *   indices     device int64 (tokens x top_k): the expert of each pair, 0 <= index < num_groups <= 256 (a pair with
+ *               any other index belongs to no expert: it gets no row and pos = 0)
+ *   weights     device fp32 (tokens x top_k): the routing weight of each pair
+ *   rows        size of the sorted buffer: a multiple of 128, at least tokens*top_k + num_groups*127
+ *   offsets     out, device int32 (num_groups + 1): segment bounds
+ *   row_token   out, device int32 (rows): token of each sorted row, -1 for padding rows
+ *   pos         out, device int32 (tokens x top_k): sorted row of each pair
+ *   row_weight  out, device fp32 (rows): routing weight of each sorted row, 0 for padding rows
+ */
+int b200moe_route(const int64_t* indices, const float* weights, int32_t tokens, int32_t top_k, int32_t num_groups, int32_t rows,
+                  int32_t* offsets, int32_t* row_token, int32_t* pos, float* row_weight, int32_t device, void* stream);
+
+/*
  * out[r,:] = src[row_src[r],:] * (row_scale ? row_scale[r] : 1) for row_src[r] >= 0, zeros for
  * row_src[r] < 0 (padding rows).  Replaces `hidden_states[token_idx]` (modeling_gpt_oss.py:104);
  * with row_scale = the routing weight of each sorted row it is also the gradient of the weighted

@@ -19,7 +19,7 @@ EXPORTS = (
     "b200attn_bwd_dq", "b200attn_bwd_dq_is_fused", "b200attn_bwd_static_scratch", "b200attn_umma_selftest",
     "b200attn_wait_selftest", "b200attn_rope",
     "b200moe_sizeof_gemm_params", "b200moe_grouped_gemm", "b200moe_gather_rows", "b200moe_combine_rows", "b200moe_row_dot",
-    "b200moe_glu", "b200moe_glu_bwd", "b200moe_bias_grad",
+    "b200moe_glu", "b200moe_glu_bwd", "b200moe_bias_grad", "b200moe_route",
 )
 
 ROW_TILE = 128
@@ -122,6 +122,7 @@ def load() -> ctypes.CDLL:
             ("b200moe_glu", [vp, vp, i64, i32, i32, vp]),
             ("b200moe_glu_bwd", [vp, vp, vp, i64, i32, i32, vp]),
             ("b200moe_bias_grad", [vp, vp, vp, i32, i32, i32, vp]),
+            ("b200moe_route", [vp, vp, i32, i32, i32, i32, vp, vp, vp, vp, i32, vp]),
         ):
             fn = getattr(lib, name)
             fn.restype = ctypes.c_int

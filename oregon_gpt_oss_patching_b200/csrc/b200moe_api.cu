@@ -208,4 +208,26 @@ int b200moe_bias_grad(const void* dy, const int32_t* offsets, void* db, int32_t 
   return launch_status();
 }
 
+int b200moe_route(const int64_t* indices, const float* weights, int32_t tokens, int32_t top_k, int32_t num_groups, int32_t rows,
+                  int32_t* offsets, int32_t* row_token, int32_t* pos, float* row_weight, int32_t device, void* stream) {
+  if (indices == nullptr || weights == nullptr || offsets == nullptr || row_token == nullptr || pos == nullptr || row_weight == nullptr)
+    return B200ATTN_EINVAL;
+  if (tokens <= 0 || top_k <= 0 || num_groups <= 0 || num_groups > kRouteMaxGroups) return B200ATTN_ESHAPE;
+  const long long pairs = (long long)tokens * top_k;
+  // room for any routing: every group may waste up to 127 rows
+  if (rows % B200MOE_ROW_ALIGN != 0 || rows < pairs + (long long)num_groups * (B200MOE_ROW_ALIGN - 1) || pairs > (1ll << 30))
+    return B200ATTN_ESHAPE;
+  int rc = check_device(device);
+  if (rc) return rc;
+  DeviceGuard guard(device);
+  if (!guard.ok) return B200ATTN_ECUDA;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (cudaMemsetAsync(row_token, 0xff, (size_t)rows * sizeof(int32_t), st) != cudaSuccess ||      // -1: padding row
+      cudaMemsetAsync(row_weight, 0, (size_t)rows * sizeof(float), st) != cudaSuccess)
+    return B200ATTN_ECUDA;
+  moe_route_kernel<<<1, kRouteThreads, 0, st>>>(reinterpret_cast<const long long*>(indices), weights, (int)pairs, top_k, num_groups,
+                                                   offsets, row_token, pos, row_weight);
+  return launch_status();
+}
+
 }  // extern "C"

@@ -187,4 +187,91 @@ moe_bias_grad_kernel(const __nv_bfloat16* __restrict__ dy, const int* __restrict
   }
 }
 
+// Routing bookkeeping in one launch of one CTA: the (token, choice) pairs sorted by expert (stable: inside an expert
+// the pairs keep their order), every expert's segment starting at a multiple of 128 rows.  Stands in for the
+// `one_hot` / `nonzero` / `torch.where` bookkeeping of GptOssExperts.forward (modeling_gpt_oss.py:86-103), which
+// synchronises with the host once per expert.  Warp w owns the contiguous pairs [w * chunk, (w + 1) * chunk) and
+// walks them 32 at a time (coalesced loads, the next batch's in flight under this one's bookkeeping):
+//   1. count: the lanes of a batch that share an expert find each other (`match.any`), the lowest of them adds
+//      their number to the warp's counter of that expert (shared memory, one column per warp);
+//   2. one warp per expert turns the 32 counts into exclusive prefix sums (the warp's first row inside the
+//      expert's segment) and the expert's total;
+//   3. thread 0 lays the segments out (totals rounded up to 128);
+//   4. the same walk again: a pair's row is segment start + the warp's running count + the number of lower lanes
+//      of the batch with the same expert; row_token / row_weight are written at that row and the row into pos.
+// row_token and row_weight must hold -1 / 0 for the padding rows before the launch (the entry point clears them).
+constexpr int kRouteThreads = 1024;
+constexpr int kRouteWarps = kRouteThreads / 32;
+constexpr int kRouteAlign = 128;
+constexpr int kRouteMaxGroups = 256;
+__global__ void __launch_bounds__(kRouteThreads)
+moe_route_kernel(const long long* __restrict__ indices, const float* __restrict__ weights, int pairs, int top_k, int num_groups,
+                 int* __restrict__ offsets, int* __restrict__ row_token, int* __restrict__ pos, float* __restrict__ row_weight) {
+  __shared__ int cnt[kRouteMaxGroups][kRouteWarps + 1];   // counts, then first rows inside the segment (+1: no bank conflicts in step 2)
+  __shared__ int seg_start[kRouteMaxGroups + 1];
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int chunk = ((pairs + kRouteWarps - 1) / kRouteWarps + 31) / 32 * 32;   // whole batches per warp
+  const int p0 = min(warp * chunk, pairs), p1 = min(p0 + chunk, pairs);
+  for (int i = tid; i < num_groups * (kRouteWarps + 1); i += kRouteThreads) (&cnt[0][0])[i] = 0;
+  __syncthreads();
+  // an index out of range is no expert's pair: it gets no row
+  auto expert_of = [&](int p) -> int {
+    if (p >= p1) return -1;
+    const int e = (int)indices[p];
+    return (unsigned)e < (unsigned)num_groups ? e : -1;
+  };
+  int e_next = expert_of(p0 + lane);
+  for (int p = p0; p < p1; p += 32) {
+    const int e = e_next;
+    e_next = expert_of(p + 32 + lane);
+    const uint32_t same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0 && lane == __ffs(same) - 1) cnt[e][warp] += __popc(same);
+    __syncwarp();   // the next batch's leader of this expert may be another lane
+  }
+  __syncthreads();
+  for (int e = warp; e < num_groups; e += kRouteWarps) {
+    const int c = cnt[e][lane];
+    int incl = c;
+#pragma unroll
+    for (int off = 1; off < 32; off <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, incl, off);
+      if (lane >= off) incl += up;
+    }
+    cnt[e][lane] = incl - c;
+    if (lane == 31) seg_start[e + 1] = incl;   // the expert's total, for now
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int acc = 0;
+    seg_start[0] = 0;
+    offsets[0] = 0;
+    for (int e = 0; e < num_groups; ++e) {
+      acc += (seg_start[e + 1] + kRouteAlign - 1) / kRouteAlign * kRouteAlign;
+      seg_start[e + 1] = acc;
+      offsets[e + 1] = acc;
+    }
+  }
+  __syncthreads();
+  e_next = expert_of(p0 + lane);
+  float w_next = p0 + lane < p1 ? weights[p0 + lane] : 0.f;
+  for (int p = p0; p < p1; p += 32) {
+    const int e = e_next;
+    const float w = w_next;
+    e_next = expert_of(p + 32 + lane);
+    w_next = p + 32 + lane < p1 ? weights[p + 32 + lane] : 0.f;
+    const uint32_t same = __match_any_sync(0xffffffffu, e);
+    if (e >= 0) {
+      const int row = seg_start[e] + cnt[e][warp] + __popc(same & ((1u << lane) - 1u));
+      row_token[row] = (p + lane) / top_k;
+      row_weight[row] = w;
+      pos[p + lane] = row;
+    } else if (p + lane < p1) {
+      pos[p + lane] = 0;
+    }
+    __syncwarp();
+    if (e >= 0 && lane == __ffs(same) - 1) cnt[e][warp] += __popc(same);
+    __syncwarp();
+  }
+}
+
 }  // namespace b200moe

@@ -14,8 +14,8 @@ as grouped GEMMs on the tensor cores over token rows sorted by expert, behind th
                bias gradients as per-expert column sums, d w[t, j] = <d out[t], Y2[row of (t, j)]>
 
 The routing bookkeeping (a stable sort of the (token, choice) pairs by expert, segment offsets rounded up
-to 128 rows) is a handful of torch tensor operations with no host synchronisation; everything that touches
-activations or weights is one of this library's kernels.  There is no other code path: if the library is
+to 128 rows) is one more launch (``b200moe_route``; ``route`` states the same thing in torch tensor operations and
+serves the CPU tests); nothing synchronises with the host.  There is no other code path: if the library is
 missing or rejects a call an exception is raised.
 
 Differences from the Hugging Face loop, all deliberate: sums over a token's experts and over an expert's
@@ -33,7 +33,7 @@ import torch
 from . import _cabi
 from .attention_kernel import _status_word
 
-__all__ = ["moe_experts", "b200_experts_forward", "patch_moe_experts", "unpatch_moe_experts", "route", "padded_rows",
+__all__ = ["moe_experts", "b200_experts_forward", "patch_moe_experts", "unpatch_moe_experts", "route", "route_on_device", "padded_rows",
            "set_gemm_ctas"]
 
 
@@ -75,6 +75,25 @@ def route(router_indices: torch.Tensor, routing_weights: torch.Tensor, num_exper
     row_weight = torch.zeros(rows, dtype=torch.float32, device=dev)
     row_weight[dest] = routing_weights.reshape(-1).to(torch.float32)[order]
     return Routing(offsets.to(torch.int32), row_token, pos.view(T, k), row_weight, rows)
+
+
+ROUTE_KERNEL_MAX_EXPERTS = 256
+
+
+def route_on_device(router_indices: torch.Tensor, weights_f32: torch.Tensor, num_experts: int) -> Routing:
+    """The same bookkeeping as ``route`` in one launch of this library (``b200moe_route``): bit-identical outputs."""
+    T, k = router_indices.shape
+    dev = router_indices.device
+    rows = padded_rows(T * k, num_experts)
+    idx = router_indices.to(torch.int64).contiguous()
+    offsets = torch.empty(num_experts + 1, dtype=torch.int32, device=dev)
+    row_token = torch.empty(rows, dtype=torch.int32, device=dev)
+    pos = torch.empty(T, k, dtype=torch.int32, device=dev)
+    row_weight = torch.empty(rows, dtype=torch.float32, device=dev)
+    rc = _cabi.load().b200moe_route(_ptr(idx), _ptr(weights_f32), T, k, num_experts, rows, _ptr(offsets), _ptr(row_token), _ptr(pos),
+                                    _ptr(row_weight), dev.index, _stream(dev))
+    _cabi.check(rc, "b200moe_route")
+    return Routing(offsets, row_token, pos, row_weight, rows)
 
 
 def _ptr(t):
@@ -136,7 +155,9 @@ class _moe_experts(torch.autograd.Function):
         E, _, I2 = w1.shape
         I = I2 // 2
         k = router_indices.shape[1]
-        r = route(router_indices, routing_weights, E)
+        weights = routing_weights.to(torch.float32).contiguous()
+        r = (route_on_device(router_indices, weights, E) if E <= ROUTE_KERNEL_MAX_EXPERTS
+             else route(router_indices, routing_weights, E))
         rows, di, st = r.rows, dev.index, _stream(dev)
         bf = dict(dtype=torch.bfloat16, device=dev)
         xs = torch.empty(rows, H, **bf)
@@ -150,7 +171,6 @@ class _moe_experts(torch.autograd.Function):
             _cabi.check(lib.b200moe_glu(_ptr(y1), _ptr(h), rows, I, di, st), "b200moe_glu")
         y2 = torch.empty(rows, H, **bf)
         grouped_gemm(_cabi.MOE_ROWS_NN, h, w2, y2, r.offsets, bias=b2, N=H, K=I)
-        weights = routing_weights.to(torch.float32).contiguous()
         out = torch.empty(T, H, **bf)
         _cabi.check(lib.b200moe_combine_rows(_ptr(y2), _ptr(r.pos), _ptr(weights), _ptr(out), T, k, H, di, st), "b200moe_combine_rows")
         ctx.save_for_backward(xs, y1, h, y2, w1, w2, r.offsets, r.row_token, r.pos, r.row_weight)

@@ -101,6 +101,28 @@ def test_grouped_gemm_inner_tn(counts, M, N):
     assert last_status(DEV) == 0
 
 
+@pytest.mark.parametrize("tokens,top_k,experts,skew", [(8192, 4, 32, False), (1, 4, 32, False), (3000, 2, 128, False),
+                                                        (40000, 4, 8, True), (257, 3, 5, True)])
+def test_routing_kernel_matches_the_tensor_operations_bit_for_bit(tokens, top_k, experts, skew):
+    """`b200moe_route` (one launch) against `route` (a stable argsort and prefix sums in torch): the same offsets, the
+    same row for every pair, the same padding rows.  `skew` sends most pairs to one expert and leaves another empty."""
+    from oregon_gpt_oss_patching_b200.moe_experts import route_on_device
+    g = torch.Generator().manual_seed(tokens + experts)
+    logits = torch.randn(tokens, experts, generator=g)
+    if skew:
+        logits[:, 0] += 6.0
+        logits[:, experts - 1] = -1e9
+    val, idx = torch.topk(logits, top_k, dim=-1)
+    weights = torch.softmax(val, -1).to(DEV)
+    idx = idx.to(DEV)
+    ref = route(idx, weights, experts)
+    got = route_on_device(idx, weights.float().contiguous(), experts)
+    torch.cuda.synchronize()
+    assert got.rows == ref.rows
+    assert torch.equal(got.offsets, ref.offsets) and torch.equal(got.pos, ref.pos)
+    assert torch.equal(got.row_token, ref.row_token) and torch.equal(got.row_weight, ref.row_weight)
+
+
 def _banded(shape, band=4096):
     """A tensor of `shape` carved out of the middle of a larger allocation filled with a sentinel; returns (view, whole)."""
     n = 1
