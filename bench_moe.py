@@ -4,8 +4,8 @@
 Workload: the gpt-oss-20b layer (hidden 2880, intermediate 2880, 32 experts, 4 per token) on `--moe-tokens`
 tokens (default 8192 = one sequence of the fine-tuning configuration), random bf16 weights, routing from
 random logits (nearly balanced; stated because real routers are not).  A step is `moe_experts` forward and
-backward: 14 launches of this library's kernels (6 grouped GEMMs -- the first forward one also writes the gated
-activation -- and 8 memory-bound ones).
+backward: 15 launches of this library's kernels (6 grouped GEMMs -- the first forward one also writes the gated
+activation -- 8 memory-bound ones and the routing kernel).
 
 `value` counts the algorithmic FLOPs of the six matrix products over the real (token, choice) pairs,
 2 * pairs * 3 * H * I each for forward, input gradient and weight gradient; `roofline` is the grouped GEMM
@@ -216,7 +216,7 @@ def run_moe(args, rank, world, local_rank):
         "clocks": clocks,
         "e2e": {"value": round(flops / (ms_e2e * 1e-3) / 1e12, 2), "unit": "TFLOP/s", "ms_per_step": round(ms_e2e, 3),
                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
-        "gpu_launches": 14 * steps,
+        "gpu_launches": 15 * steps,
         "roofline": {"bound": "tensor", "achieved": round(achieved, 1), "peak": peaks["bf16_tflops"], "unit": "TFLOP/s",
                      "frac": round(achieved / peaks["bf16_tflops"], 4), "kernel": "moe_grouped_gemm_kernel (six launches per step)",
                      "peak_source": peaks["source"], "traffic": None},
